@@ -1,0 +1,160 @@
+/*
+ * soliton_b200 -- C ABI of libsoliton_b200.so
+ *
+ * A B200-native replacement for one path of Soliton (vishesh9131/soliton): the data-parallel gradient mean
+ * (NCCL ncclAvg in the reference), the 1/world scaling and the AdamW update, fused into one family of sm_100a
+ * kernels that exchange gradients through NVSwitch peer loads and stores.
+ *
+ * Three groups of entry points:
+ *   1. `sl_*`       -- the functions Soliton's Python binds through ctypes (python/soliton/_C.py:11-67) that lie on
+ *                      the path or that the path's callers need around it (allocator, device, data movement).
+ *                      Same names, argument meaning, return codes and error channel as core/soliton/api.d.
+ *   2. `sl_cuda_*`  -- the backend functions Soliton's D core declares (core/soliton/api.d:10-65) and its CUDA file
+ *                      defines for this path. A Soliton build links these in place of the originals.
+ *   3. `slb_*`      -- additions without a counterpart in the reference (options, counters, test hooks).
+ *
+ * Conventions (core/soliton/alloc.d:12, python/soliton/tensor.py:22-23): dev 0 = cpu, 1 = meta, 2 = cuda.
+ * On meta every function does the same allocator traffic as on cuda and no device work. Compute entry points
+ * called with dev = 0 set sticky error 13: this library has no host kernels. All device work is enqueued on the
+ * legacy default stream, as in the reference; nothing throws; one thread per process.
+ * Sticky error codes read by sl_check: 1..11 as in core/cuda/kernels.cu:21-34,101-108 (2 launch, 3 sync);
+ * 12 bad argument, 13 compute on cpu, 14 device not initialised through sl_init_device,
+ * 21/22/23 a bounded device-side wait on a peer rank ran out (start / reduced / done barrier).
+ */
+#ifndef SOLITON_B200_H
+#define SOLITON_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------ 1. sl_*: memory (the allocator contract) */
+
+/* core/soliton/api.d:133-136 (Pool.alloc, core/soliton/alloc.d:128-174). NULL when out of memory / diverged. */
+void* sl_alloc(int dev, size_t n);
+/* core/soliton/api.d:138-141 (Pool.release, alloc.d:176-200). n is the unrounded size given to sl_alloc. */
+void sl_free(int dev, void* p, size_t n);
+/* core/soliton/api.d:143-154. out: allocated, reserved, peak_allocated, peak_reserved, n_alloc, n_raw, trace_hash */
+void sl_stats(int dev, int64_t* out7);
+/* core/soliton/api.d:156-164 */
+void sl_reset_stats(int dev);
+/* core/soliton/api.d:166-169 */
+void sl_empty_cache(int dev);
+/* core/soliton/api.d:256-260. 0 = unlimited. */
+void sl_set_limit(int dev, int64_t bytes);
+/* core/soliton/api.d:173-215: trace recording for the arena planner */
+void sl_record_start(int dev);
+void sl_record_stop(int dev);
+void sl_record_mark(int dev);
+int64_t sl_record_count(int dev);
+int64_t sl_record_body(int dev);
+void sl_record_get(int dev, int64_t* size, int64_t* start, int64_t* end);
+/* core/soliton/api.d:217-238. The two arrays stay owned by the caller and must outlive the install. 0 or -2. */
+int sl_arena_install(int dev, const int64_t* offsets, const int64_t* sizes, int64_t count, int64_t body,
+                     int64_t arena_bytes);
+/* core/soliton/api.d:240-244 */
+int sl_arena_diverged(int dev);
+/* core/soliton/api.d:246-254 */
+void sl_arena_off(int dev);
+
+/* ------------------------------------------------------------------ sl_*: device */
+
+/* core/soliton/api.d:262-274. cpu: 0. meta and cuda: reserves, from the pool, the reference's 32 MiB BLAS
+ * workspace and then this library's 18 MiB data-parallel workspace (flag words, segment tables, one-shot
+ * staging) -- the only scratch the path ever uses, taken once and in this fixed order on both devices, so a meta
+ * dry run predicts the cuda pool exactly. 0, -1 (no such device) or -2 (out of memory). */
+int sl_init_device(int dev, int ordinal);
+/* core/soliton/api.d:275-278 */
+int sl_cuda_count(void);
+/* core/soliton/api.d:280-283. Sticky error code, 0 when none. */
+int sl_check(int dev);
+/* core/soliton/api.d:285-289. Launches whatever step is pending, then waits for the device. */
+void sl_sync(int dev);
+/* core/soliton/api.d:299-302 */
+void sl_mem_info(size_t* free_bytes, size_t* total_bytes);
+
+/* ------------------------------------------------------------------ sl_*: data movement (blocking, as the reference) */
+
+/* core/soliton/api.d:313-326 */
+void sl_from_host(int dev, void* dst, const void* src, size_t n);
+void sl_to_host(int dev, void* dst, const void* src, size_t n);
+void sl_copy(int dev, void* dst, const void* src, size_t n);
+/* core/soliton/api.d:330-333 */
+void sl_fill(int dev, float* p, int64_t n, float v);
+
+/* ------------------------------------------------------------------ sl_*: the path */
+
+/* core/soliton/api.d:539-543 -> core/cuda/kernels.cu:242-254. One AdamW update of p, m, v (n floats each) with
+ * gradient g. On cuda the call is recorded and launched together with its neighbours (see sl_dist_group). */
+void sl_adamw(int dev, float* p, const float* g, float* m, float* v, int64_t n, float lr, float b1, float b2,
+              float eps, float wd, int step);
+/* core/soliton/api.d:572-575 -> core/cuda/kernels.cu:761-766. Rank 0: fills 128 bytes that name the group. */
+int sl_dist_unique_id(char* out128);
+/* core/soliton/api.d:577-580 -> core/cuda/kernels.cu:767-771. After sl_init_device(2, ordinal). 0 or -1. */
+int sl_dist_init(int rank, int world, const char* id128);
+/* core/soliton/api.d:582-585 -> core/cuda/kernels.cu:772. start=1 opens a group, start=0 closes it; closing
+ * meets the peers on the host (bounded) and arms one fused launch for all gradients of the group. 0 or -1. */
+int sl_dist_group(int dev, int start);
+/* core/soliton/api.d:587-590 -> core/cuda/kernels.cu:773-775. In place mean over ranks of n floats at p. 0 or -1. */
+int sl_dist_allreduce_mean(int dev, float* p, int64_t n);
+/* core/soliton/api.d:592-595 -> core/cuda/kernels.cu:776-779 */
+void sl_dist_destroy(void);
+
+/* ------------------------------------------------------------------ sl_*: next to the path (gradient clipping, accumulation) */
+
+/* core/soliton/api.d:363-376 (python/soliton/optim.py:31-39 uses sumsq + scale; tensor.py:451-462 uses axpy) */
+void sl_axpy(int dev, const float* x, float* y, int64_t n, float alpha);
+void sl_scale(int dev, const float* x, float* y, int64_t n, float alpha);
+/* core/soliton/api.d:378-382. Blocking. NaN on meta. */
+double sl_sumsq(int dev, const float* x, int64_t n);
+
+/* ------------------------------------------------------------------ 2. sl_cuda_*: backend level */
+
+/* core/soliton/api.d:47-48 -> core/cuda/kernels.cu:251-254 */
+void sl_cuda_adamw(float* p, const float* g, float* m, float* v, int64_t n, float lr, float b1, float b2, float eps,
+                   float wd, int step);
+/* core/soliton/api.d:58-62 -> core/cuda/kernels.cu:761-779 */
+int sl_cuda_nccl_unique_id(char* out128);
+int sl_cuda_nccl_init(int rank, int world, const char* id128);
+int sl_cuda_nccl_group(int start);
+int sl_cuda_nccl_allreduce_mean(float* p, int64_t n);
+void sl_cuda_nccl_destroy(void);
+/* No counterpart in the reference; modelled on sl_cuda_set_workspace (core/cuda/kernels.cu:115). A host core that
+ * owns the allocator hands the path its workspace (slb_workspace_bytes() bytes from its pool) once per device. */
+int sl_cuda_dp_set_workspace(void* p, size_t n);
+
+/* ------------------------------------------------------------------ 3. slb_*: no counterpart in the reference */
+
+size_t slb_workspace_bytes(void);
+/* Options: "eager" (0/1), "mode" (0 auto, 1 one-shot, 2 two-shot), "blocks_per_sm", "timeout_ms" (device waits),
+ * "host_timeout_ms", "oneshot_max_bytes" (-1: whatever fits the staging slots). Must be set alike on all ranks.
+ * Returns 0, or -1 for an unknown name. */
+int slb_set_option(const char* name, int64_t value);
+/* Counters: "launches" (kernels of this library launched so far), "last_mode" (0 local, 1 one-shot, 2 two-shot),
+ * "last_blocks", "world", "sm_count". -1 for an unknown name. */
+int64_t slb_get_counter(const char* name);
+/* Clears the sticky error (after a test provoked one on purpose). */
+void slb_clear_error(void);
+/* The partition the kernels use: tiles of the step, and the tile range [*begin, *end) that block `block` of
+ * `blocks` works on inside chunk `chunk` of `world` (chunk = -1: inside the whole sequence). */
+int64_t slb_tile_count(const int64_t* n, int nseg);
+void slb_run_range(int64_t tiles, int world, int chunk, int blocks, int block, int64_t* begin, int64_t* end);
+/* Test hook: `world` ranks emulated on one GPU by one cooperative launch (blocks of all ranks resident together).
+ * Pointer arrays are indexed [rank * nseg + segment]; p/m/v may be NULL when adam = 0. mode: 0 auto, 1 one-shot,
+ * 2 two-shot. active_mask: bit r set = rank r takes part (a missing rank makes the others' waits run out).
+ * status_out[world] receives each rank's device status (0, or 21/22/23). Returns 0 or a negative code. */
+int slb_sim_step(int world, int nseg, const int64_t* n, float* const* p, float* const* g, float* const* m,
+                 float* const* v, const float* wd, float lr, float b1, float b2, float eps, int step, int adam,
+                 int mode, int blocks_per_rank, int64_t timeout_ms, unsigned active_mask, int* status_out);
+/* Test hook: runs the host rendezvous protocol (no CUDA) as rank `rank` of `world` for `rounds` collectives with
+ * synthetic tables and checks what it reads from the peers. 0 when everything matched. */
+int slb_rdv_selftest(const char* id128, int rank, int world, int rounds);
+int slb_rdv_create_id(char* out128);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SOLITON_B200_H */

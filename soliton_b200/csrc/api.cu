@@ -1,0 +1,251 @@
+// The C ABI of libsoliton_b200.so (declared in include/soliton_b200.h): routing by device kind, as
+// core/soliton/api.d does it. meta does the allocator traffic and nothing else; cuda goes to the engine; cpu is
+// served for memory and data movement only -- compute on cpu raises sticky error 13, this library has no host
+// kernels to fall back to.
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstring>
+#include <vector>
+
+#include "../../include/soliton_b200.h"
+#include "dp_engine.hpp"
+#include "pool.hpp"
+
+using namespace slb;
+
+static Engine& E() { return Engine::get(); }
+static inline void before_memory_op(int dev) {
+    if (dev == DEV_CUDA) E().flush();  // nothing pending may outlive memory it points into
+}
+
+extern "C" {
+
+// ---- memory
+
+void* sl_alloc(int dev, size_t n) { return valid_dev(dev) ? pool(dev).alloc(n) : nullptr; }
+
+void sl_free(int dev, void* p, size_t n) {
+    if (!valid_dev(dev)) return;
+    before_memory_op(dev);
+    pool(dev).release(p, n);
+}
+
+void sl_stats(int dev, int64_t* out7) {
+    if (valid_dev(dev)) pool(dev).stats(out7);
+}
+void sl_reset_stats(int dev) {
+    if (valid_dev(dev)) pool(dev).reset_stats();
+}
+void sl_empty_cache(int dev) {
+    if (!valid_dev(dev)) return;
+    before_memory_op(dev);
+    pool(dev).empty_cache();
+}
+void sl_set_limit(int dev, int64_t bytes) {
+    if (valid_dev(dev)) pool(dev).set_limit(bytes);
+}
+void sl_record_start(int dev) {
+    if (valid_dev(dev)) pool(dev).record_start();
+}
+void sl_record_stop(int dev) {
+    if (valid_dev(dev)) pool(dev).record_stop();
+}
+void sl_record_mark(int dev) {
+    if (valid_dev(dev)) pool(dev).record_mark();
+}
+int64_t sl_record_count(int dev) { return valid_dev(dev) ? pool(dev).record_count() : 0; }
+int64_t sl_record_body(int dev) { return valid_dev(dev) ? pool(dev).record_body() : 0; }
+void sl_record_get(int dev, int64_t* size, int64_t* start, int64_t* end) {
+    if (valid_dev(dev)) pool(dev).record_get(size, start, end);
+}
+int sl_arena_install(int dev, const int64_t* offsets, const int64_t* sizes, int64_t count, int64_t body,
+                     int64_t arena_bytes) {
+    if (!valid_dev(dev)) return -1;
+    before_memory_op(dev);
+    return pool(dev).arena_install(offsets, sizes, count, body, arena_bytes);
+}
+int sl_arena_diverged(int dev) { return valid_dev(dev) && pool(dev).diverged() ? 1 : 0; }
+void sl_arena_off(int dev) {
+    if (!valid_dev(dev)) return;
+    before_memory_op(dev);
+    pool(dev).arena_off();
+}
+
+// ---- device
+
+int sl_init_device(int dev, int ordinal) { return E().init_device(dev, ordinal); }
+int sl_cuda_count(void) { return E().device_count(); }
+int sl_check(int dev) {
+    const int e = E().check();
+    return dev == DEV_CUDA || e == ERR_NO_CPU_COMPUTE ? e : 0;
+}
+void sl_sync(int dev) {
+    if (dev == DEV_CUDA) E().sync();
+}
+void sl_mem_info(size_t* free_bytes, size_t* total_bytes) {
+    if (cudaMemGetInfo(free_bytes, total_bytes) != cudaSuccess) {
+        cudaGetLastError();
+        *free_bytes = *total_bytes = 0;
+    }
+}
+
+// ---- data movement
+
+static void copy_any(int dev, void* dst, const void* src, size_t n, cudaMemcpyKind kind) {
+    if (n == 0) return;
+    if (dev == DEV_CPU) {
+        memcpy(dst, src, n);
+    } else if (dev == DEV_CUDA) {
+        E().flush();
+        if (cudaMemcpy(dst, src, n, kind) != cudaSuccess) E().set_error(ERR_SYNC);
+    }
+}
+void sl_from_host(int dev, void* dst, const void* src, size_t n) { copy_any(dev, dst, src, n, cudaMemcpyHostToDevice); }
+void sl_to_host(int dev, void* dst, const void* src, size_t n) { copy_any(dev, dst, src, n, cudaMemcpyDeviceToHost); }
+void sl_copy(int dev, void* dst, const void* src, size_t n) { copy_any(dev, dst, src, n, cudaMemcpyDeviceToDevice); }
+
+void sl_fill(int dev, float* p, int64_t n, float v) {
+    if (dev == DEV_CPU) {
+        for (int64_t i = 0; i < n; i++) p[i] = v;  // initialisation of host buffers, not a compute kernel
+    } else if (dev == DEV_CUDA) {
+        E().fill(p, n, v);
+    }
+}
+
+// ---- the path
+
+void sl_adamw(int dev, float* p, const float* g, float* m, float* v, int64_t n, float lr, float b1, float b2,
+              float eps, float wd, int step) {
+    if (dev == DEV_CUDA)
+        E().adamw(p, g, m, v, n, lr, b1, b2, eps, wd, step);
+    else if (dev == DEV_CPU)
+        E().set_error(ERR_NO_CPU_COMPUTE);
+}
+int sl_dist_unique_id(char* out128) { return E().dist_unique_id(out128); }
+int sl_dist_init(int rank, int world, const char* id128) { return E().dist_init(rank, world, id128); }
+int sl_dist_group(int dev, int start) { return dev == DEV_CUDA ? E().group(start) : 0; }
+int sl_dist_allreduce_mean(int dev, float* p, int64_t n) { return dev == DEV_CUDA ? E().allreduce_mean(p, n) : 0; }
+void sl_dist_destroy(void) { E().dist_destroy(); }
+
+// ---- next to the path
+
+void sl_axpy(int dev, const float* x, float* y, int64_t n, float alpha) {
+    if (dev == DEV_CUDA)
+        E().axpy(x, y, n, alpha);
+    else if (dev == DEV_CPU)
+        E().set_error(ERR_NO_CPU_COMPUTE);
+}
+void sl_scale(int dev, const float* x, float* y, int64_t n, float alpha) {
+    if (dev == DEV_CUDA)
+        E().scale(x, y, n, alpha);
+    else if (dev == DEV_CPU)
+        E().set_error(ERR_NO_CPU_COMPUTE);
+}
+double sl_sumsq(int dev, const float* x, int64_t n) {
+    if (dev == DEV_CUDA) return E().sumsq(x, n);
+    if (dev == DEV_CPU) E().set_error(ERR_NO_CPU_COMPUTE);
+    return NAN;
+}
+
+// ---- backend level
+
+void sl_cuda_adamw(float* p, const float* g, float* m, float* v, int64_t n, float lr, float b1, float b2, float eps,
+                   float wd, int step) {
+    E().adamw(p, g, m, v, n, lr, b1, b2, eps, wd, step);
+}
+int sl_cuda_nccl_unique_id(char* out128) { return E().dist_unique_id(out128); }
+int sl_cuda_nccl_init(int rank, int world, const char* id128) { return E().dist_init(rank, world, id128); }
+int sl_cuda_nccl_group(int start) { return E().group(start); }
+int sl_cuda_nccl_allreduce_mean(float* p, int64_t n) { return E().allreduce_mean(p, n); }
+void sl_cuda_nccl_destroy(void) { E().dist_destroy(); }
+int sl_cuda_dp_set_workspace(void* p, size_t n) { return E().adopt_workspace(p, n); }
+
+// ---- additions
+
+size_t slb_workspace_bytes(void) { return kWorkspaceBytes; }
+
+int slb_set_option(const char* name, int64_t value) {
+    Options& o = E().opt;
+    if (!name) return -1;
+    if (!strcmp(name, "eager")) o.eager = (int)value;
+    else if (!strcmp(name, "mode")) o.mode = (int)value;
+    else if (!strcmp(name, "blocks_per_sm")) o.blocks_per_sm = (int)value;
+    else if (!strcmp(name, "timeout_ms")) o.timeout_ns = (unsigned long long)value * 1000000ull;
+    else if (!strcmp(name, "host_timeout_ms")) o.host_timeout_s = (double)value / 1000.0;
+    else if (!strcmp(name, "oneshot_max_bytes")) o.oneshot_max_bytes = value;
+    else return -1;
+    return 0;
+}
+
+int64_t slb_get_counter(const char* name) {
+    if (!name) return -1;
+    if (!strcmp(name, "launches")) return (int64_t)E().launches;
+    if (!strcmp(name, "last_mode")) return E().last_mode;
+    if (!strcmp(name, "last_blocks")) return E().last_blocks;
+    if (!strcmp(name, "world")) return E().world();
+    if (!strcmp(name, "sm_count")) return E().sm_count();
+    return -1;
+}
+
+void slb_clear_error(void) { E().clear_error(); }
+
+int64_t slb_tile_count(const int64_t* n, int nseg) {
+    int64_t t = 0;
+    for (int s = 0; s < nseg; s++) t += (n[s] + kTile - 1) / kTile;
+    return t;
+}
+
+void slb_run_range(int64_t tiles, int world, int chunk, int blocks, int block, int64_t* begin, int64_t* end) {
+    int64_t cb = 0, ce = tiles;
+    if (chunk >= 0) cb = tiles * chunk / world, ce = tiles * (chunk + 1) / world;
+    const int64_t len = ce - cb;
+    *begin = cb + len * block / blocks;
+    *end = cb + len * (block + 1) / blocks;
+}
+
+int slb_sim_step(int world, int nseg, const int64_t* n, float* const* p, float* const* g, float* const* m,
+                 float* const* v, const float* wd, float lr, float b1, float b2, float eps, int step, int adam,
+                 int mode, int blocks_per_rank, int64_t timeout_ms, unsigned active_mask, int* status_out) {
+    return E().sim_step(world, nseg, n, p, g, m, v, wd, lr, b1, b2, eps, step, adam, mode, blocks_per_rank,
+                        (unsigned long long)timeout_ms * 1000000ull, active_mask, status_out);
+}
+
+int slb_rdv_create_id(char* out128) { return Rendezvous::create_id(out128); }
+
+int slb_rdv_selftest(const char* id128, int rank, int world, int rounds) {
+    Rendezvous r;
+    const double wait_s = E().opt.host_timeout_s;
+    if (r.open(id128, rank, world, wait_s) != 0) return -1;
+    int rc = 0;
+    if (r.stage_barrier(1, wait_s) != 0) rc = -2;
+    // Round k: rank q publishes nseg = 3 + (k / 2) % 2 segments {export q, offset 1000 q + 16 (k / 2) + s, n = 7 s + 1},
+    // so tables change every second round and the unchanged rounds must not bump the version.
+    uint64_t last_version[kRdvMaxWorld] = {0};
+    for (int k = 1; rc == 0 && k <= rounds; k++) {
+        const uint32_t nseg = 3 + (k / 2) % 2;
+        std::vector<RdvSegment> t(nseg);
+        for (uint32_t s = 0; s < nseg; s++) t[s] = RdvSegment{(uint32_t)rank, 0, (uint64_t)(1000 * rank + 16 * (k / 2) + s), (int64_t)(7 * s + 1)};
+        if (r.arrive((uint64_t)k, t.data(), nseg, wait_s) != 0) {
+            rc = -3;
+            break;
+        }
+        for (int q = 0; q < world; q++) {
+            uint32_t n2 = 0;
+            uint64_t ver = 0;
+            const RdvSegment* pt = r.table_of(q, (uint64_t)k, &n2, &ver);
+            if (n2 != nseg) rc = -4;
+            for (uint32_t s = 0; rc == 0 && s < nseg; s++)
+                if (pt[s].export_id != (uint32_t)q || pt[s].offset != (uint64_t)(1000 * q + 16 * (k / 2) + s) || pt[s].n != (int64_t)(7 * s + 1)) rc = -5;
+            const bool should_change = k == 1 || (k % 2 == 0);
+            if (rc == 0 && should_change != (ver != last_version[q])) rc = -6;
+            last_version[q] = ver;
+        }
+    }
+    if (rc != 0) r.fail();
+    if (r.stage_barrier(2, wait_s) != 0 && rc == 0) rc = -7;
+    r.close();
+    return rc;
+}
+
+}  // extern "C"

@@ -1,0 +1,466 @@
+// sm_100a kernels of the data-parallel optimizer path: gradient mean over ranks + AdamW, in one launch.
+//
+// Replaces, for this path, the reference's ncclAllReduce(ncclAvg) (core/cuda/kernels.cu:773-775) followed by one
+// k_adamw launch per tensor (core/cuda/kernels.cu:242-254).
+//
+// The path is bandwidth-bound (28 algorithmic HBM bytes per parameter, no contraction), so the kernels are built
+// around memory traffic: 128-bit coalesced accesses, every thread issuing all loads of a tile before it touches
+// the data (2 x (3 + ranks) independent 16-byte loads per thread), streaming cache hints for local tensors, one
+// launch for all tensors of a step, and grids sized to the number of blocks that are resident at once.
+// Peer gradients are read and written directly through NVSwitch-mapped pointers; no library collective runs.
+//
+//   k_twoshot<W,ADAM>  reduce-scatter + all-gather. Rank c owns chunk c of the tile sequence: it pulls that chunk
+//                      from every rank, sums in rank order 0..W-1, multiplies by 1/W, stores the mean into its own
+//                      gradient and (ADAM) updates its own p, m, v on the spot. Then it pulls every other chunk's
+//                      mean from its owner, stores it into its local gradient and updates p, m, v there.
+//                      With W == 1 this is the plain multi-tensor AdamW step.
+//   k_oneshot<W,ADAM>  for small steps: every rank pushes its gradients into a staging slot on every peer, one
+//                      barrier, then every rank reduces all W copies locally in the same rank order.
+//
+// Both produce the same bits: the sum is ((g0 + g1) + g2) + ... in float, then one multiply by 1/W, whoever
+// computes it; so weights stay bit-identical across ranks and across the one-shot/two-shot choice.
+//
+// Synchronisation is per block index: block b of a rank only ever depends on block b of its peers, because the
+// run of tiles block b works on inside a chunk is the same on every rank. Flag words are monotonic in the launch
+// sequence number, written with st.release.sys and polled with ld.acquire.sys; every poll loop is bounded by
+// LaunchArgs::timeout_ns, after which the block records a status code, skips its remaining data work, still posts
+// its own flags (so peers do not wait on it in turn) and returns normally.
+#include <cuda_runtime.h>
+
+#include "dp_launch.h"
+#include "dp_types.h"
+
+namespace slb {
+
+enum Mode : int { REDUCE_OWN = 0, GATHER = 1, PUSH = 2, REDUCE_STAGED = 3 };
+enum Barrier : int { B_START = 0, B_REDUCED = 1, B_DONE = 2 };
+
+// ---------------------------------------------------------------- memory primitives
+
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+// Gradient data that another GPU may have written during this launch (or that lives on another GPU): strong
+// system-scope loads, which never hit a stale L1 line. Ordered after the acquiring flag poll by program order.
+__device__ __forceinline__ float4 ld_sys4(const float* p) {
+    float4 v;
+    asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "l"(p)
+                 : "memory");
+    return v;
+}
+__device__ __forceinline__ float ld_sys1(const float* p) {
+    float v;
+    asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+    return v;
+}
+// Local tensors that are read once and written once per step: streaming (evict-first) accesses.
+__device__ __forceinline__ float4 ld_stream4(const float* p) { return __ldcs(reinterpret_cast<const float4*>(p)); }
+__device__ __forceinline__ void st_stream4(float* p, float4 v) { __stcs(reinterpret_cast<float4*>(p), v); }
+
+// ---------------------------------------------------------------- AdamW arithmetic
+
+// One element of the reference update (core/cuda/kernels.cu:242-250) with every rounding written out, so that the
+// result does not depend on how a compiler contracts the expression: m and v in float with the products feeding
+// an FMA, bias-corrected moments and the quotient in IEEE double, wd * p rounded in float before it is promoted,
+// one final rounding of p to float.
+__device__ __forceinline__ void adamw_elem(float& p, float g, float& m, float& v, const Hyper& h, float wd) {
+    m = __fmaf_rn(h.b1, m, __fmul_rn(h.c1, g));
+    v = __fmaf_rn(h.b2, v, __fmul_rn(__fmul_rn(h.c2, g), g));
+    const double mh = __ddiv_rn((double)m, h.bc1);
+    const double vh = __ddiv_rn((double)v, h.bc2);
+    const double x = __dadd_rn(__ddiv_rn(mh, __dadd_rn(__dsqrt_rn(vh), (double)h.eps)), (double)__fmul_rn(wd, p));
+    p = __double2float_rn(__fma_rn(-(double)h.lr, x, (double)p));
+}
+__device__ __forceinline__ void adamw_vec(float4& p, const float4& g, float4& m, float4& v, const Hyper& h, float wd) {
+    adamw_elem(p.x, g.x, m.x, v.x, h, wd);
+    adamw_elem(p.y, g.y, m.y, v.y, h, wd);
+    adamw_elem(p.z, g.z, m.z, v.z, h, wd);
+    adamw_elem(p.w, g.w, m.w, v.w, h, wd);
+}
+__device__ __forceinline__ float4 add4(const float4& a, const float4& b) {
+    return make_float4(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y), __fadd_rn(a.z, b.z), __fadd_rn(a.w, b.w));
+}
+__device__ __forceinline__ float4 mul4(const float4& a, float s) {
+    return make_float4(__fmul_rn(a.x, s), __fmul_rn(a.y, s), __fmul_rn(a.z, s), __fmul_rn(a.w, s));
+}
+
+// ---------------------------------------------------------------- segment lookup
+
+// The segment a block is currently inside, held in registers; refilled only when a tile leaves its range.
+template <int W>
+struct SegView {
+    float *p, *m, *v;
+    float* g[W];   // REDUCE_OWN: every rank's gradient
+    float* gme;    // this rank's gradient
+    float* gsrc;   // GATHER: the owner's gradient
+    int64_t n;
+    float wd;
+    int hyper, vec;
+    int first_tile, end_tile;  // [first, end) of this segment in the tile sequence
+};
+
+// Largest s with prefix[s] <= t (segments without elements share their successor's prefix and are skipped).
+__device__ __forceinline__ int find_seg(const int* prefix, int nseg, int t) {
+    int lo = 0, hi = nseg;  // invariant: prefix[lo] <= t < prefix[hi]
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (prefix[mid] <= t)
+            lo = mid;
+        else
+            hi = mid;
+    }
+    return lo;
+}
+
+template <int W>
+__device__ __forceinline__ void load_seg(SegView<W>& s, const RankCtx& c, const int* prefix, int t, int me, int src) {
+    const int i = find_seg(prefix, c.nseg, t);
+    const Seg* sg = c.segs + i;
+    s.p = sg->p, s.m = sg->m, s.v = sg->v;
+#pragma unroll
+    for (int r = 0; r < W; r++) s.g[r] = sg->g[r];
+    s.gme = sg->g[me];
+    s.gsrc = sg->g[src];
+    s.n = sg->n, s.wd = sg->wd, s.hyper = sg->hyper, s.vec = sg->vec;
+    s.first_tile = prefix[i], s.end_tile = prefix[i + 1];
+}
+
+// ---------------------------------------------------------------- one tile
+
+// Processes tile t of the sequence in the given mode. `stage` (one-shot only) is the base of the staging half in
+// use on this rank; peers' halves come from c.stage[r] + stage_off.
+template <int W, bool ADAM, int MODE>
+__device__ __forceinline__ void do_tile(const SegView<W>& s, const LaunchArgs& a, const RankCtx& c, int t, int me,
+                                        const float* stage, size_t stage_off) {
+    const int tid = threadIdx.x;
+    const int64_t base = (int64_t)(t - s.first_tile) * kTile;
+    const int64_t left = s.n - base;
+    const int cnt = left < kTile ? (int)left : kTile;
+    const int slot = a.stage_slot_floats;
+    const Hyper& h = a.hp[s.hyper];
+    const bool adam = ADAM && s.p != nullptr;
+    constexpr int U = kTile / (4 * kThreads);
+
+    if (s.vec && cnt == kTile) {
+        float4 gv[U][W], pv[U], mv[U], vv[U];
+        // every load of the tile is issued before the first use
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const int e = (tid + u * kThreads) * 4;
+            const int64_t off = base + e;
+            if (MODE == REDUCE_OWN) {
+                if (W == 1) {
+                    gv[u][0] = ld_stream4(s.gme + off);
+                } else {
+#pragma unroll
+                    for (int r = 0; r < W; r++) gv[u][r] = ld_sys4(s.g[r] + off);
+                }
+            } else if (MODE == GATHER) {
+                gv[u][0] = ld_sys4(s.gsrc + off);
+            } else if (MODE == REDUCE_STAGED) {
+#pragma unroll
+                for (int r = 0; r < W; r++)
+                    gv[u][r] = r == me ? ld_sys4(s.gme + off) : ld_sys4(stage + (size_t)r * slot + (size_t)t * kTile + e);
+            } else {
+                gv[u][0] = ld_stream4(s.gme + off);
+            }
+            if (MODE != PUSH && adam) {
+                pv[u] = ld_stream4(s.p + off);
+                mv[u] = ld_stream4(s.m + off);
+                vv[u] = ld_stream4(s.v + off);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const int e = (tid + u * kThreads) * 4;
+            const int64_t off = base + e;
+            if (MODE == PUSH) {
+#pragma unroll
+                for (int r = 0; r < W; r++)
+                    if (r != me)
+                        *reinterpret_cast<float4*>(c.stage[r] + stage_off + (size_t)me * slot + (size_t)t * kTile + e) =
+                            gv[u][0];
+                continue;
+            }
+            float4 avg = gv[u][0];
+            if (MODE != GATHER && W > 1) {
+#pragma unroll
+                for (int r = 1; r < W; r++) avg = add4(avg, gv[u][r]);
+                avg = mul4(avg, a.inv_world);
+            }
+            if (W > 1) st_stream4(s.gme + off, avg);
+            if (adam) {
+                adamw_vec(pv[u], avg, mv[u], vv[u], h, s.wd);
+                st_stream4(s.p + off, pv[u]);
+                st_stream4(s.m + off, mv[u]);
+                st_stream4(s.v + off, vv[u]);
+            }
+        }
+    } else {
+        // partial tiles (a segment's tail, tensors smaller than a tile) and unaligned tensors: one float at a time
+        for (int e = tid; e < cnt; e += kThreads) {
+            const int64_t off = base + e;
+            if (MODE == PUSH) {
+                const float x = s.gme[off];
+#pragma unroll
+                for (int r = 0; r < W; r++)
+                    if (r != me) c.stage[r][stage_off + (size_t)me * slot + (size_t)t * kTile + e] = x;
+                continue;
+            }
+            float avg;
+            if (MODE == GATHER) {
+                avg = ld_sys1(s.gsrc + off);
+            } else if (W == 1) {
+                avg = s.gme[off];
+            } else {
+                float x[W];
+#pragma unroll
+                for (int r = 0; r < W; r++) {
+                    if (MODE == REDUCE_OWN)
+                        x[r] = ld_sys1(s.g[r] + off);
+                    else
+                        x[r] = r == me ? ld_sys1(s.gme + off) : ld_sys1(stage + (size_t)r * slot + (size_t)t * kTile + e);
+                }
+                avg = x[0];
+#pragma unroll
+                for (int r = 1; r < W; r++) avg = __fadd_rn(avg, x[r]);
+                avg = __fmul_rn(avg, a.inv_world);
+            }
+            if (W > 1) s.gme[off] = avg;
+            if (adam) {
+                float p = s.p[off], m = s.m[off], v = s.v[off];
+                adamw_elem(p, avg, m, v, h, s.wd);
+                s.p[off] = p, s.m[off] = m, s.v[off] = v;
+            }
+        }
+    }
+}
+
+template <int W, bool ADAM, int MODE>
+__device__ __forceinline__ void do_run(const LaunchArgs& a, const RankCtx& c, const int* prefix, int t0, int t1, int me,
+                                       int src, const float* stage, size_t stage_off) {
+    SegView<W> s;
+    s.first_tile = 0, s.end_tile = 0;
+    for (int t = t0; t < t1; t++) {
+        if (t >= s.end_tile || t < s.first_tile) load_seg<W>(s, c, prefix, t, me, src);
+        do_tile<W, ADAM, MODE>(s, a, c, t, me, stage, stage_off);
+    }
+}
+
+// ---------------------------------------------------------------- flag barriers
+
+__device__ __forceinline__ size_t flag_index(int barrier, int block, int src) {
+    return ((size_t)barrier * kFlagBlocks + block) * kMaxWorld + src;
+}
+
+// Tell every peer that this block of this rank reached `barrier` in launch `seq`.
+template <int W>
+__device__ __forceinline__ void post(const RankCtx& c, int barrier, int block, int me, unsigned seq) {
+    __syncthreads();  // all of the block's stores come before the release below
+    const int r = threadIdx.x;
+    if (r < W && r != me) {
+        __threadfence_system();
+        st_release_sys(c.flags[r] + flag_index(barrier, block, me), seq);
+    }
+}
+
+// Wait (bounded) until rank `src` posted `barrier` for this block index. src < 0 waits for every peer.
+template <int W>
+__device__ __forceinline__ void await(const RankCtx& c, const LaunchArgs& a, int barrier, int block, int me, int src,
+                                      int code, int* s_abort) {
+    const int r = threadIdx.x;
+    if (r < W && r != me && (src < 0 || r == src)) {
+        const unsigned* f = c.flags[me] + flag_index(barrier, block, r);
+        const unsigned long long t0 = global_ns();
+        while ((int)(ld_acquire_sys(f) - a.seq) < 0) {
+            if (global_ns() - t0 > a.timeout_ns) {
+                atomicCAS(c.status, 0, code);
+                *s_abort = 1;
+                break;
+            }
+            __nanosleep(32);
+        }
+    }
+    __syncthreads();
+}
+
+__device__ __forceinline__ int cut(int total, int part, int parts) { return (int)((int64_t)total * part / parts); }
+
+// ---------------------------------------------------------------- kernels
+
+template <int W, bool ADAM>
+__global__ void __launch_bounds__(kThreads, 2) k_twoshot(const __grid_constant__ LaunchArgs a) {
+    extern __shared__ int s_prefix[];
+    __shared__ int s_abort;
+    const int G = a.blocks_per_rank;
+    const int b = blockIdx.x % G;
+    const RankCtx& c = a.ctxs[blockIdx.x / G];
+    const int me = c.rank, nseg = c.nseg;
+    for (int i = threadIdx.x; i <= nseg; i += kThreads) s_prefix[i] = c.tile_prefix[i];
+    if (threadIdx.x == 0) s_abort = 0;
+    __syncthreads();
+    const int T = s_prefix[nseg];
+
+    if (W > 1) {
+        post<W>(c, B_START, b, me, a.seq);
+        await<W>(c, a, B_START, b, me, -1, ST_TIMEOUT_START, &s_abort);
+    }
+    {   // own chunk: reduce, scale, update
+        const int cb = cut(T, me, W), ce = cut(T, me + 1, W), L = ce - cb;
+        if (!s_abort) do_run<W, ADAM, REDUCE_OWN>(a, c, s_prefix, cb + cut(L, b, G), cb + cut(L, b + 1, G), me, me, nullptr, 0);
+    }
+    if (W > 1) {
+        post<W>(c, B_REDUCED, b, me, a.seq);
+        for (int k = 1; k < W; k++) {  // other chunks, starting after the own one so that owners are hit evenly
+            const int src = (me + k) % W;
+            await<W>(c, a, B_REDUCED, b, me, src, ST_TIMEOUT_REDUCED, &s_abort);
+            const int cb = cut(T, src, W), ce = cut(T, src + 1, W), L = ce - cb;
+            if (!s_abort) do_run<W, ADAM, GATHER>(a, c, s_prefix, cb + cut(L, b, G), cb + cut(L, b + 1, G), me, src, nullptr, 0);
+        }
+        // nobody may reuse or free gradient memory that a peer is still reading
+        post<W>(c, B_DONE, b, me, a.seq);
+        await<W>(c, a, B_DONE, b, me, -1, ST_TIMEOUT_DONE, &s_abort);
+    }
+}
+
+template <int W, bool ADAM>
+__global__ void __launch_bounds__(kThreads, 2) k_oneshot(const __grid_constant__ LaunchArgs a) {
+    extern __shared__ int s_prefix[];
+    __shared__ int s_abort;
+    const int G = a.blocks_per_rank;
+    const int b = blockIdx.x % G;
+    const RankCtx& c = a.ctxs[blockIdx.x / G];
+    const int me = c.rank, nseg = c.nseg;
+    for (int i = threadIdx.x; i <= nseg; i += kThreads) s_prefix[i] = c.tile_prefix[i];
+    if (threadIdx.x == 0) s_abort = 0;
+    __syncthreads();
+    const int T = s_prefix[nseg];
+    const int t0 = cut(T, b, G), t1 = cut(T, b + 1, G);
+    // Staging is double-buffered by launch parity: a peer that already runs the next one-shot launch writes the
+    // other half, and it cannot be two launches ahead because it waits for this rank's flag in between.
+    const size_t stage_off = (size_t)a.parity * W * a.stage_slot_floats;
+    do_run<W, ADAM, PUSH>(a, c, s_prefix, t0, t1, me, me, nullptr, stage_off);
+    post<W>(c, B_REDUCED, b, me, a.seq);
+    await<W>(c, a, B_REDUCED, b, me, -1, ST_TIMEOUT_REDUCED, &s_abort);
+    if (!s_abort) do_run<W, ADAM, REDUCE_STAGED>(a, c, s_prefix, t0, t1, me, me, c.stage[me] + stage_off, stage_off);
+}
+
+// ---------------------------------------------------------------- small elementwise kernels next to the path
+
+// y = alpha * x (core/cuda/kernels.cu:208-212), y += alpha * x (sl_cuda_axpy), p = value (k_fill, :127-131).
+__global__ void __launch_bounds__(kThreads) k_scale(int64_t n, const float* x, float* y, float alpha) {
+    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += (int64_t)gridDim.x * kThreads)
+        y[i] = __fmul_rn(alpha, x[i]);
+}
+__global__ void __launch_bounds__(kThreads) k_axpy(int64_t n, const float* x, float* y, float alpha) {
+    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += (int64_t)gridDim.x * kThreads)
+        y[i] = __fmaf_rn(alpha, x[i], y[i]);
+}
+__global__ void __launch_bounds__(kThreads) k_fill(int64_t n, float* p, float value) {
+    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += (int64_t)gridDim.x * kThreads)
+        p[i] = value;
+}
+
+// Sum of squares, deterministic: block b owns the fixed slice [n*b/B, n*(b+1)/B), a thread accumulates its strided
+// elements in double, warps combine by shuffle in a fixed tree, warp results are added in warp order.
+__global__ void __launch_bounds__(kThreads) k_sumsq(int64_t n, const float* x, double* partials) {
+    __shared__ double s_warp[kThreads / 32];
+    const int64_t lo = n / gridDim.x * blockIdx.x + (n % gridDim.x) * blockIdx.x / gridDim.x;
+    const int64_t hi = n / gridDim.x * (blockIdx.x + 1) + (n % gridDim.x) * (blockIdx.x + 1) / gridDim.x;
+    double acc = 0;
+    for (int64_t i = lo + threadIdx.x; i < hi; i += kThreads) {
+        const double v = (double)x[i];
+        acc = __fma_rn(v, v, acc);
+    }
+    for (int o = 16; o; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
+    if ((threadIdx.x & 31) == 0) s_warp[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double t = 0;
+        for (int w = 0; w < kThreads / 32; w++) t += s_warp[w];
+        partials[blockIdx.x] = t;
+    }
+}
+
+// ---------------------------------------------------------------- launch
+
+template <int W, bool ADAM>
+static cudaError_t launch_w(bool oneshot, bool cooperative, int grid, size_t smem, const LaunchArgs& a, cudaStream_t st) {
+    void (*kern)(const LaunchArgs) = oneshot ? k_oneshot<W, ADAM> : k_twoshot<W, ADAM>;
+    if (cooperative) {
+        void* params[] = {const_cast<LaunchArgs*>(&a)};
+        return cudaLaunchCooperativeKernel((const void*)kern, dim3(grid), dim3(kThreads), params, smem, st);
+    }
+    kern<<<grid, kThreads, smem, st>>>(a);
+    return cudaPeekAtLastError();
+}
+
+template <int W, bool ADAM>
+static int occupancy_w(bool oneshot, size_t smem) {
+    int n = 0;
+    void (*kern)(const LaunchArgs) = oneshot ? k_oneshot<W, ADAM> : k_twoshot<W, ADAM>;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, (const void*)kern, kThreads, smem) != cudaSuccess) return 0;
+    return n;
+}
+
+#define SLB_DISPATCH(W_, fn, ...)                                        \
+    switch (W_) {                                                        \
+        case 1: return adam ? fn<1, true>(__VA_ARGS__) : fn<1, false>(__VA_ARGS__); \
+        case 2: return adam ? fn<2, true>(__VA_ARGS__) : fn<2, false>(__VA_ARGS__); \
+        case 3: return adam ? fn<3, true>(__VA_ARGS__) : fn<3, false>(__VA_ARGS__); \
+        case 4: return adam ? fn<4, true>(__VA_ARGS__) : fn<4, false>(__VA_ARGS__); \
+        case 5: return adam ? fn<5, true>(__VA_ARGS__) : fn<5, false>(__VA_ARGS__); \
+        case 6: return adam ? fn<6, true>(__VA_ARGS__) : fn<6, false>(__VA_ARGS__); \
+        case 7: return adam ? fn<7, true>(__VA_ARGS__) : fn<7, false>(__VA_ARGS__); \
+        case 8: return adam ? fn<8, true>(__VA_ARGS__) : fn<8, false>(__VA_ARGS__); \
+    }
+
+int launch_step(int world, bool adam, bool oneshot, bool cooperative, int grid, size_t smem, const LaunchArgs& a,
+                cudaStream_t st) {
+    SLB_DISPATCH(world, launch_w, oneshot, cooperative, grid, smem, a, st)
+    return (int)cudaErrorInvalidValue;
+}
+
+int step_occupancy(int world, bool adam, bool oneshot, size_t smem) {
+    SLB_DISPATCH(world, occupancy_w, oneshot, smem)
+    return 0;
+}
+
+static int flat_grid(int64_t n) {
+    int64_t g = (n + kThreads - 1) / kThreads;
+    return (int)(g < 1 ? 1 : g > 148 * 8 ? 148 * 8 : g);
+}
+int launch_scale(const float* x, float* y, int64_t n, float alpha, cudaStream_t st) {
+    if (n <= 0) return 0;
+    k_scale<<<flat_grid(n), kThreads, 0, st>>>(n, x, y, alpha);
+    return (int)cudaPeekAtLastError();
+}
+int launch_axpy(const float* x, float* y, int64_t n, float alpha, cudaStream_t st) {
+    if (n <= 0) return 0;
+    k_axpy<<<flat_grid(n), kThreads, 0, st>>>(n, x, y, alpha);
+    return (int)cudaPeekAtLastError();
+}
+int launch_fill(float* p, int64_t n, float value, cudaStream_t st) {
+    if (n <= 0) return 0;
+    k_fill<<<flat_grid(n), kThreads, 0, st>>>(n, p, value);
+    return (int)cudaPeekAtLastError();
+}
+
+int launch_sumsq_partials(const float* x, int64_t n, double* partials, int blocks, cudaStream_t st) {
+    k_sumsq<<<blocks, kThreads, 0, st>>>(n, x, partials);
+    return (int)cudaPeekAtLastError();
+}
+
+}  // namespace slb
