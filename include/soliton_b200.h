@@ -136,6 +136,8 @@ int slb_set_option(const char* name, int64_t value);
 /* Counters: "launches" (kernels of this library launched so far), "last_mode" (0 local, 1 one-shot, 2 two-shot),
  * "last_blocks", "world", "sm_count". -1 for an unknown name. */
 int64_t slb_get_counter(const char* name);
+/* Launches whatever step is pending without waiting for the device (sl_sync does the same and then waits). */
+void slb_flush(void);
 /* Clears the sticky error (after a test provoked one on purpose). */
 void slb_clear_error(void);
 /* The partition the kernels use: tiles of the step, and the tile range [*begin, *end) that block `block` of

@@ -63,6 +63,7 @@ _SIGS = {
     "slb_workspace_bytes": (S, []),
     "slb_set_option": (I, [C.c_char_p, L]),
     "slb_get_counter": (L, [C.c_char_p]),
+    "slb_flush": (None, []),
     "slb_clear_error": (None, []),
     "slb_tile_count": (L, [LP, I]),
     "slb_run_range": (None, [L, I, I, I, I, LP, LP]),

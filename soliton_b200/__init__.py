@@ -2,7 +2,14 @@
 
 The package holds only what that path needs: the CUDA/C++ library (csrc/, built by soliton_b200.build), its ctypes
 binding, and thin mirrors of the Soliton Python interfaces that call into the path (optim, distributed, tensor).
+Submodules load on first use, so that `python -m soliton_b200.build` works before the library exists.
 """
-from . import distributed, optim, tensor, workload  # noqa: F401
-from .tensor import (empty, empty_cache, memory_stats, reset_peak_stats, set_device, set_memory_limit,  # noqa: F401
-                     synchronize, tensor as from_numpy, zeros)
+import importlib
+
+_SUBMODULES = ("build", "distributed", "optim", "tensor", "workload", "_C")
+
+
+def __getattr__(name):
+    if name in _SUBMODULES:
+        return importlib.import_module(f"{__name__}.{name}")
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

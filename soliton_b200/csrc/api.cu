@@ -188,6 +188,7 @@ int64_t slb_get_counter(const char* name) {
     return -1;
 }
 
+void slb_flush(void) { E().flush(); }
 void slb_clear_error(void) { E().clear_error(); }
 
 int64_t slb_tile_count(const int64_t* n, int nseg) {
