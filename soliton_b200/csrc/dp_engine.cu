@@ -234,6 +234,7 @@ static void fill_hyper(Hyper& h, const HyperKey& k) {
     // core/cuda/kernels.cu:253: 1.0 - pow(b, step) with both arguments promoted to double
     h.bc1 = 1.0 - std::pow((double)k.b1, (double)k.step);
     h.bc2 = 1.0 - std::pow((double)k.b2, (double)k.step);
+    h.rbc1 = 1.0 / h.bc1, h.rbc2 = 1.0 / h.bc2;
     h.lr = k.lr, h.b1 = k.b1, h.b2 = k.b2, h.eps = k.eps;
     h.c1 = 1 - k.b1, h.c2 = 1 - k.b2;
 }
@@ -265,6 +266,13 @@ static int64_t build_table(const std::vector<StepItem>& items, int world, int ra
     return tiles;
 }
 
+// Capacity of one (parity, source rank) staging slot: the staging area holds 2 x world of them. Whole tiles, so
+// that every slot starts 16-byte aligned whatever the world size.
+static int stage_slot_floats(int world) {
+    const size_t raw = kStageBytes / 4 / (2 * (size_t)(world > 1 ? world : 1));
+    return (int)(raw / kTile * kTile);
+}
+
 static int min_chunk(int T, int world) {
     int best = T;
     for (int c = 0; c < world; c++) {
@@ -284,7 +292,7 @@ int Engine::launch_items(std::vector<StepItem>& items, const std::vector<HyperKe
     if (T < 0) return ERR_BAD_ARG;
     const int nseg = (int)items.size();
 
-    const int slot_floats = (int)(kStageBytes / 4 / (2 * (size_t)(W > 1 ? W : 1)));
+    const int slot_floats = stage_slot_floats(W);
     bool oneshot = false;
     if (W > 1) {
         const bool fits = T * kTile <= slot_floats;
@@ -617,7 +625,7 @@ int Engine::sim_step(int world, int nseg, const int64_t* n, float* const* p, flo
     if (ctxs.empty()) return -1;
     if (cudaMemcpyAsync(sim_ws_, ctxs.data(), ctxs.size() * sizeof(RankCtx), cudaMemcpyHostToDevice, 0) != cudaSuccess) return -1;
 
-    const int slot_floats = (int)(kStageBytes / 4 / (2 * (size_t)(world > 1 ? world : 1)));
+    const int slot_floats = stage_slot_floats(world);
     const bool fits = T * kTile <= slot_floats;
     bool oneshot = world > 1 && fits && (mode == 1 || (mode == 0 && T * kTile * 4 <= (opt.oneshot_max_bytes < 0 ? INT64_MAX : opt.oneshot_max_bytes)));
     if (mode == 1 && !oneshot) return -4;  // asked for one-shot, but the step does not fit the staging slots

@@ -71,16 +71,63 @@ __device__ __forceinline__ void st_stream4(float* p, float4 v) { __stcs(reinterp
 
 // ---------------------------------------------------------------- AdamW arithmetic
 
+// Branch-free double-precision building blocks. CUDA's own IEEE division and square root carry a range check with
+// a slow path, and that branch keeps the compiler from interleaving the eight independent elements a thread holds.
+// The operands here are floats promoted to double and bias corrections in (0, 1], far from the exponent limits,
+// so the checked range is not needed. Each routine ends in FMA residual corrections that make the result the
+// correctly rounded one (Markstein's construction); the GPU tests compare every bit with IEEE division / sqrt.
+__device__ __forceinline__ double rcp_seed(double d) {
+    double y;
+    asm("rcp.approx.ftz.f64 %0, %1;" : "=d"(y) : "d"(d));
+    return y;
+}
+__device__ __forceinline__ double rsqrt_seed(double x) {
+    double y;
+    asm("rsqrt.approx.ftz.f64 %0, %1;" : "=d"(y) : "d"(x));
+    return y;
+}
+// a / b with y = RN(1 / b) supplied (b is a launch constant; the host rounds its reciprocal correctly).
+__device__ __forceinline__ double div_by_const(double a, double b, double y) {
+    double q = __dmul_rn(a, y);
+    double r = __fma_rn(-b, q, a);
+    q = __fma_rn(r, y, q);      // faithful
+    r = __fma_rn(-b, q, a);
+    return __fma_rn(r, y, q);   // correctly rounded
+}
+__device__ __forceinline__ double div_exact(double a, double d) {
+    double y = rcp_seed(d);                     // ~20 bits
+    double e = __fma_rn(-d, y, 1.0);
+    y = __fma_rn(y, e, y);                      // ~40 bits
+    e = __fma_rn(-d, y, 1.0);
+    y = __fma_rn(y, e, y);                      // full precision, within an ulp
+    e = __fma_rn(-d, y, 1.0);
+    y = __fma_rn(y, e, y);                      // RN(1 / d)
+    return div_by_const(a, d, y);
+}
+__device__ __forceinline__ double sqrt_exact(double x) {
+    const double y = rsqrt_seed(x);             // ~20 bits of 1 / sqrt(x)
+    double g = __dmul_rn(x, y), h = __dmul_rn(0.5, y);
+    double r = __fma_rn(-g, h, 0.5);
+    g = __fma_rn(g, r, g), h = __fma_rn(h, r, h);
+    r = __fma_rn(-g, h, 0.5);
+    g = __fma_rn(g, r, g), h = __fma_rn(h, r, h);
+    double rem = __fma_rn(-g, g, x);
+    g = __fma_rn(rem, h, g);
+    rem = __fma_rn(-g, g, x);
+    g = __fma_rn(rem, h, g);
+    return x == 0.0 ? 0.0 : g;                  // the seed of 0 is inf; sqrt(0) is 0
+}
+
 // One element of the reference update (core/cuda/kernels.cu:242-250) with every rounding written out, so that the
 // result does not depend on how a compiler contracts the expression: m and v in float with the products feeding
-// an FMA, bias-corrected moments and the quotient in IEEE double, wd * p rounded in float before it is promoted,
-// one final rounding of p to float.
+// an FMA, bias-corrected moments and the quotient in correctly rounded double, wd * p rounded in float before it
+// is promoted, one final rounding of p to float.
 __device__ __forceinline__ void adamw_elem(float& p, float g, float& m, float& v, const Hyper& h, float wd) {
     m = __fmaf_rn(h.b1, m, __fmul_rn(h.c1, g));
     v = __fmaf_rn(h.b2, v, __fmul_rn(__fmul_rn(h.c2, g), g));
-    const double mh = __ddiv_rn((double)m, h.bc1);
-    const double vh = __ddiv_rn((double)v, h.bc2);
-    const double x = __dadd_rn(__ddiv_rn(mh, __dadd_rn(__dsqrt_rn(vh), (double)h.eps)), (double)__fmul_rn(wd, p));
+    const double mh = div_by_const((double)m, h.bc1, h.rbc1);
+    const double vh = div_by_const((double)v, h.bc2, h.rbc2);
+    const double x = __dadd_rn(div_exact(mh, __dadd_rn(sqrt_exact(vh), (double)h.eps)), (double)__fmul_rn(wd, p));
     p = __double2float_rn(__fma_rn(-(double)h.lr, x, (double)p));
 }
 __device__ __forceinline__ void adamw_vec(float4& p, const float4& g, float4& m, float4& v, const Hyper& h, float wd) {
@@ -300,8 +347,10 @@ __device__ __forceinline__ int cut(int total, int part, int parts) { return (int
 
 // ---------------------------------------------------------------- kernels
 
+// Resident blocks per SM the single-rank kernel is compiled for (80 registers per thread).
+constexpr int kLocalBlocksPerSm = 3;
 template <int W, bool ADAM>
-__global__ void __launch_bounds__(kThreads, 2) k_twoshot(const __grid_constant__ LaunchArgs a) {
+__global__ void __launch_bounds__(kThreads, W == 1 ? kLocalBlocksPerSm : 2) k_twoshot(const __grid_constant__ LaunchArgs a) {
     extern __shared__ int s_prefix[];
     __shared__ int s_abort;
     const int G = a.blocks_per_rank;

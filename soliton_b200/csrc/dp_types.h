@@ -12,8 +12,9 @@
 namespace slb {
 
 constexpr int kMaxWorld = 8;        // ranks of one NVSwitch box
-constexpr int kTile = 2048;         // floats per tile (8 KiB per tensor stream)
-constexpr int kThreads = 256;       // threads per block; each handles kTile / (4 * kThreads) = 2 float4 per tile
+constexpr int kThreads = 256;       // threads per block
+constexpr int kVecPerThread = 2;    // float4 vectors per thread, tensor stream and tile
+constexpr int kTile = 4 * kThreads * kVecPerThread;  // floats per tile: 2048 (8 KiB per tensor stream)
 constexpr int kMaxSegs = 4096;      // segments per step
 constexpr int kMaxHyper = 8;        // distinct hyperparameter sets per step
 constexpr int kFlagBlocks = 2048;   // upper bound on blocks per rank that take part in flag barriers
@@ -35,6 +36,7 @@ static_assert(kPartialOff + kSumsqBlocks * 8 <= kCtlBytes, "control area layout"
 
 struct Hyper {  // one AdamW hyperparameter set of a step (core/cuda/kernels.cu:251-254 computes bc1, bc2 on the host)
     double bc1, bc2;        // 1 - b1^step, 1 - b2^step, in double
+    double rbc1, rbc2;      // their correctly rounded reciprocals
     float lr, b1, b2, eps;
     float c1, c2;           // the floats (1 - b1), (1 - b2)
 };

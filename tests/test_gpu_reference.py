@@ -54,6 +54,31 @@ def test_five_steps_bit_identical_to_reference_kernel(ref, hyper):
             np.testing.assert_array_equal(c, want)    # and the GPU-shaped oracle restates that kernel exactly
 
 
+def test_special_values_bit_identical_to_reference_kernel(ref):
+    # Zero gradients (v = 0: square root of zero), gradients whose square is a float denormal, very large
+    # gradients: the inputs on which a hand-written division / square root would first differ from IEEE.
+    n = 1 << 20
+    rng = np.random.default_rng(21)
+    p0 = (rng.standard_normal(n) * 0.02).astype(np.float32)
+    p0[::13] = 0
+    g0 = (rng.standard_normal(n) * 1e-3).astype(np.float32)
+    g0[::7] = 0
+    g0[1::1001] = 1e-22
+    g0[2::1003] = 3e4
+    g0[3::1007] = -1e-30
+    g0[4::1009] = 1e15
+    h = dict(lr=3e-4, b1=0.9, b2=0.999, eps=1e-8, wd=0.1)
+    g = DevBuf(g0)
+    ours, theirs = [DevBuf(p0), zeros(n), zeros(n)], [DevBuf(p0), zeros(n), zeros(n)]
+    for step in (1, 2, 3):
+        lib.sl_adamw(CUDA, ours[0].ptr, g.ptr, ours[1].ptr, ours[2].ptr, n, h["lr"], h["b1"], h["b2"], h["eps"], h["wd"], step)
+        check_ok()
+        ref.sl_cuda_adamw(theirs[0].ptr, g.ptr, theirs[1].ptr, theirs[2].ptr, n, h["lr"], h["b1"], h["b2"], h["eps"], h["wd"], step)
+        ref.sl_cuda_sync()
+        for a, b in zip(ours, theirs):
+            np.testing.assert_array_equal(a.get().view(np.uint32), b.get().view(np.uint32))
+
+
 def test_config0_against_reference_kernel(ref):
     n = 1 << 20
     p0, g0 = workload.flat_case(n)
