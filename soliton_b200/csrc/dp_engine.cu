@@ -299,14 +299,19 @@ int Engine::launch_items(std::vector<StepItem>& items, const std::vector<HyperKe
         const bool small = opt.oneshot_max_bytes < 0 || T * kTile * 4 <= opt.oneshot_max_bytes;
         oneshot = fits && (opt.mode == 1 || (opt.mode == 0 && small));
     }
-    const size_t smem = (size_t)(nseg + 1) * sizeof(int);
+    // Which kernel: the one-shot for small collectives, the shared-memory pipeline for everything else (the plain
+    // register-staged kernel only when asked for, as the yardstick the pipeline is measured against).
+    const int kind = oneshot ? KERNEL_ONESHOT : (opt.pipeline ? KERNEL_STEP : KERNEL_PLAIN);
+    int stages = 0;
+    const size_t smem = kind == KERNEL_STEP ? step_smem(W, adam, nseg, &stages) : (size_t)(nseg + 1) * sizeof(int);
+    if (smem == 0) return ERR_LAUNCH;
     int per_sm;
     if (W > 1) {
         per_sm = kCollectiveBlocksPerSm;
         if (opt.blocks_per_sm > 0 && opt.blocks_per_sm < per_sm) per_sm = opt.blocks_per_sm;
-        if (step_occupancy(W, adam, oneshot, smem) < per_sm) return ERR_LAUNCH;
+        if (step_occupancy(W, adam, kind, smem) < per_sm) return ERR_LAUNCH;
     } else {
-        per_sm = step_occupancy(W, adam, oneshot, smem);
+        per_sm = step_occupancy(W, adam, kind, smem);
         if (opt.blocks_per_sm > 0 && opt.blocks_per_sm < per_sm) per_sm = opt.blocks_per_sm;
         if (per_sm < 1) return ERR_LAUNCH;
     }
@@ -348,11 +353,12 @@ int Engine::launch_items(std::vector<StepItem>& items, const std::vector<HyperKe
     a.stage_slot_floats = slot_floats;
     a.timeout_ns = opt.timeout_ns;
     a.inv_world = 1.0f / (float)W;
+    a.stages = stages;
     for (size_t i = 0; i < hypers.size() && i < (size_t)kMaxHyper; i++) fill_hyper(a.hp[i], hypers[i]);
     last_mode = W == 1 ? 0 : (oneshot ? 1 : 2);
     last_blocks = G;
     launches++;
-    return launch_step(W, adam, oneshot, false, G, smem, a, 0) == 0 ? 0 : ERR_LAUNCH;
+    return launch_step(W, adam, kind, false, G, smem, a, 0) == 0 ? 0 : ERR_LAUNCH;
 }
 
 // ---------------------------------------------------------------- process group
@@ -629,8 +635,11 @@ int Engine::sim_step(int world, int nseg, const int64_t* n, float* const* p, flo
     const bool fits = T * kTile <= slot_floats;
     bool oneshot = world > 1 && fits && (mode == 1 || (mode == 0 && T * kTile * 4 <= (opt.oneshot_max_bytes < 0 ? INT64_MAX : opt.oneshot_max_bytes)));
     if (mode == 1 && !oneshot) return -4;  // asked for one-shot, but the step does not fit the staging slots
-    const size_t smem = (size_t)(nseg + 1) * sizeof(int);
-    const int occ = step_occupancy(world, adam != 0, oneshot, smem);
+    const int kind = oneshot ? KERNEL_ONESHOT : (opt.pipeline ? KERNEL_STEP : KERNEL_PLAIN);
+    int stages = 0;
+    const size_t smem = kind == KERNEL_STEP ? step_smem(world, adam != 0, nseg, &stages) : (size_t)(nseg + 1) * sizeof(int);
+    if (smem == 0) return -3;
+    const int occ = step_occupancy(world, adam != 0, kind, smem);
     const int cap = occ * sm_count_ / (int)ctxs.size();
     if (cap < 1) return -3;
     const int work = (world == 1 || oneshot) ? (int)T : min_chunk((int)T, world);
@@ -646,11 +655,12 @@ int Engine::sim_step(int world, int nseg, const int64_t* n, float* const* p, flo
     a.stage_slot_floats = slot_floats;
     a.timeout_ns = timeout_ns ? timeout_ns : opt.timeout_ns;
     a.inv_world = 1.0f / (float)world;
+    a.stages = stages;
     fill_hyper(a.hp[0], HyperKey{lr, b1, b2, eps, step});
     last_mode = world == 1 ? 0 : (oneshot ? 1 : 2);
     last_blocks = G;
     launches++;
-    if (launch_step(world, adam != 0, oneshot, true, G * (int)ctxs.size(), smem, a, 0) != 0) {
+    if (launch_step(world, adam != 0, kind, true, G * (int)ctxs.size(), smem, a, 0) != 0) {
         cudaGetLastError();
         return -5;
     }

@@ -32,7 +32,7 @@
 
 namespace slb {
 
-enum Mode : int { REDUCE_OWN = 0, GATHER = 1, PUSH = 2, REDUCE_STAGED = 3 };
+enum Mode : int { REDUCE_OWN = 0, GATHER = 1, PUSH = 2, REDUCE_STAGED = 3, REDUCE_PUSH = 4, LOCAL = 5 };
 enum Barrier : int { B_START = 0, B_REDUCED = 1, B_DONE = 2 };
 
 // ---------------------------------------------------------------- memory primitives
@@ -199,8 +199,10 @@ __device__ __forceinline__ void do_tile(const SegView<W>& s, const LaunchArgs& a
     const Hyper& h = a.hp[s.hyper];
     const bool adam = ADAM && s.p != nullptr;
     constexpr int U = kTile / (4 * kThreads);
+    // REDUCE_PUSH and LOCAL only ever see the tiles the pipelined kernel leaves to this routine (partial or unaligned)
+    constexpr bool kScalarOnly = MODE == REDUCE_PUSH || MODE == LOCAL;
 
-    if (s.vec && cnt == kTile) {
+    if (!kScalarOnly && s.vec && cnt == kTile) {
         float4 gv[U][W], pv[U], mv[U], vv[U];
         // every load of the tile is issued before the first use
 #pragma unroll
@@ -269,13 +271,15 @@ __device__ __forceinline__ void do_tile(const SegView<W>& s, const LaunchArgs& a
             float avg;
             if (MODE == GATHER) {
                 avg = ld_sys1(s.gsrc + off);
+            } else if (MODE == LOCAL) {
+                avg = ld_sys1(s.gme + off);  // the owner of this chunk pushed the mean here during this launch
             } else if (W == 1) {
                 avg = s.gme[off];
             } else {
                 float x[W];
 #pragma unroll
                 for (int r = 0; r < W; r++) {
-                    if (MODE == REDUCE_OWN)
+                    if (MODE == REDUCE_OWN || MODE == REDUCE_PUSH)
                         x[r] = ld_sys1(s.g[r] + off);
                     else
                         x[r] = r == me ? ld_sys1(s.gme + off) : ld_sys1(stage + (size_t)r * slot + (size_t)t * kTile + e);
@@ -285,7 +289,12 @@ __device__ __forceinline__ void do_tile(const SegView<W>& s, const LaunchArgs& a
                 for (int r = 1; r < W; r++) avg = __fadd_rn(avg, x[r]);
                 avg = __fmul_rn(avg, a.inv_world);
             }
-            if (W > 1) s.gme[off] = avg;
+            if (MODE == REDUCE_PUSH) {
+#pragma unroll
+                for (int r = 0; r < W; r++) s.g[r][off] = avg;  // the mean goes to every rank's gradient
+            } else if (W > 1 && MODE != LOCAL) {
+                s.gme[off] = avg;
+            }
             if (adam) {
                 float p = s.p[off], m = s.m[off], v = s.v[off];
                 adamw_elem(p, avg, m, v, h, s.wd);
@@ -406,6 +415,262 @@ __global__ void __launch_bounds__(kThreads, 2) k_oneshot(const __grid_constant__
     if (!s_abort) do_run<W, ADAM, REDUCE_STAGED>(a, c, s_prefix, t0, t1, me, me, c.stage[me] + stage_off, stage_off);
 }
 
+// ---------------------------------------------------------------- shared-memory pipeline (bulk async copies)
+
+// k_step streams its tiles through a ring of shared-memory stages filled and drained by the bulk-copy engine
+// (cp.async.bulk, the untiled TMA path), so that the bytes in flight per SM are set by the ring depth and not by
+// how many loads the compute warps happen to have outstanding; that is what keeps NVLink pulls (microseconds of
+// latency) and HBM streams saturated while the warps do double-precision arithmetic. Three roles per block:
+//   warp 8, lane 0  loader:   waits for a free stage, issues one 4 KiB bulk load per input stream into it
+//   warps 0-7       compute:  wait for the stage's bytes, reduce / update in place in shared memory
+//   warp 9, lane 0  storer:   issues one bulk store per output stream (remote gradients included), frees stages
+// A pipeline step covers kSub floats of every stream (one float4 per compute thread); a tile is two steps.
+// Only whole, 16-byte aligned tiles go through the ring; ragged ends and unaligned tensors take do_tile().
+constexpr int kSub = 4 * kThreads;
+constexpr int kSubBytes = kSub * 4;
+constexpr int kSubsPerTile = kTile / kSub;
+constexpr int kMaxStages = 8;
+constexpr int kPipeThreads = kThreads + 64;
+constexpr int kPipeHeader = 256;  // mbarriers and the abort word, ahead of the tile prefix and the stages
+
+struct Pipe {
+    uint64_t *full, *computed, *empty;  // kMaxStages mbarriers each
+    int* abort;
+    unsigned char* data;
+    int stages, stage_bytes;
+};
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* b, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(b)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* b) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(b)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect(uint64_t* b, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(b)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint64_t* b, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_addr(b)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded: gives up when another role of the block already did, or after LaunchArgs::timeout_ns.
+__device__ __forceinline__ bool mbar_wait(uint64_t* b, unsigned parity, const LaunchArgs& a, const RankCtx& c,
+                                          volatile int* abort) {
+    if (mbar_try(b, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    unsigned spins = 0;
+    while (!mbar_try(b, parity)) {
+        if ((++spins & 63) == 0) {
+            if (*abort) return false;
+            if (global_ns() - t0 > a.timeout_ns) {
+                atomicCAS(c.status, 0, ST_TIMEOUT_PIPE);
+                *abort = 1;
+                return false;
+            }
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, unsigned bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_addr(smem_dst)),
+                 "l"(gsrc), "r"(bytes), "r"(smem_addr(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, unsigned bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_addr(smem_src)),
+                 "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_proxy_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// One run of tiles [t0, t1) through the pipeline. MODE REDUCE_PUSH: pull the tile from every rank, mean in rank
+// order, update own p/m/v, write the mean to every rank's gradient. MODE LOCAL: gradient already final in local
+// memory, update p/m/v. `it` counts pipeline steps over the whole kernel (stage index and mbarrier parity).
+template <int W, bool ADAM, int MODE>
+__device__ __forceinline__ void pipe_run(const LaunchArgs& a, const RankCtx& c, const Pipe& pp, const int* prefix, int t0,
+                                         int t1, int me, unsigned& it) {
+    constexpr int G = MODE == REDUCE_PUSH ? W : 1;  // gradient streams ahead of p, m, v in a stage
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    volatile int* abort = pp.abort;
+    SegView<W> s;
+    s.first_tile = 0, s.end_tile = 0;
+    unsigned my_it = it;  // every role walks the same tiles in the same order, so the counters stay equal
+
+    if (warp < kThreads / 32) {
+        // ---- compute warps
+        for (int t = t0; t < t1; t++) {
+            if (*abort) break;
+            if (t >= s.end_tile || t < s.first_tile) load_seg<W>(s, c, prefix, t, me, me);
+            const int64_t base = (int64_t)(t - s.first_tile) * kTile;
+            const bool adam = ADAM && s.p != nullptr;
+            if (MODE == LOCAL && !adam) continue;
+            if (!(s.vec && s.n - base >= kTile)) {
+                do_tile<W, ADAM, MODE>(s, a, c, t, me, nullptr, 0);
+                continue;
+            }
+            const Hyper& h = a.hp[s.hyper];
+            for (int sub = 0; sub < kSubsPerTile; sub++, my_it++) {
+                const int stage = my_it % pp.stages;
+                if (!mbar_wait(pp.full + stage, (my_it / pp.stages) & 1, a, c, abort)) break;
+                float4* st = reinterpret_cast<float4*>(pp.data + (size_t)stage * pp.stage_bytes) + threadIdx.x;
+                float4 avg = st[0];
+                if (MODE == REDUCE_PUSH) {
+#pragma unroll
+                    for (int r = 1; r < W; r++) avg = add4(avg, st[r * kThreads]);
+                    avg = mul4(avg, a.inv_world);
+                    st[0] = avg;
+                }
+                if (adam) {
+                    float4 p = st[G * kThreads], m = st[(G + 1) * kThreads], v = st[(G + 2) * kThreads];
+                    adamw_vec(p, avg, m, v, h, s.wd);
+                    st[G * kThreads] = p, st[(G + 1) * kThreads] = m, st[(G + 2) * kThreads] = v;
+                }
+                fence_async_proxy_smem();  // the bulk stores read what was just written through the generic proxy
+                mbar_arrive(pp.computed + stage);
+            }
+        }
+    } else if (warp == kThreads / 32) {
+        // ---- loader
+        if (lane == 0) {
+            fence_async_proxy();  // peers' gradients were observed through flags by generic loads; bulk loads follow
+            for (int t = t0; t < t1; t++) {
+                if (*abort) break;
+                if (t >= s.end_tile || t < s.first_tile) load_seg<W>(s, c, prefix, t, me, me);
+                const int64_t base = (int64_t)(t - s.first_tile) * kTile;
+                const bool adam = ADAM && s.p != nullptr;
+                if (MODE == LOCAL && !adam) continue;
+                if (!(s.vec && s.n - base >= kTile)) continue;
+                for (int sub = 0; sub < kSubsPerTile; sub++, my_it++) {
+                    const int stage = my_it % pp.stages;
+                    if (!mbar_wait(pp.empty + stage, ((my_it / pp.stages) & 1) ^ 1, a, c, abort)) break;
+                    unsigned char* dst = pp.data + (size_t)stage * pp.stage_bytes;
+                    const int64_t off = base + sub * kSub;
+                    mbar_arrive_expect(pp.full + stage, (unsigned)((G + (adam ? 3 : 0)) * kSubBytes));
+                    if (MODE == REDUCE_PUSH) {
+#pragma unroll
+                        for (int r = 0; r < W; r++) bulk_load(dst + r * kSubBytes, s.g[r] + off, kSubBytes, pp.full + stage);
+                    } else {
+                        bulk_load(dst, s.gme + off, kSubBytes, pp.full + stage);
+                    }
+                    if (adam) {
+                        bulk_load(dst + G * kSubBytes, s.p + off, kSubBytes, pp.full + stage);
+                        bulk_load(dst + (G + 1) * kSubBytes, s.m + off, kSubBytes, pp.full + stage);
+                        bulk_load(dst + (G + 2) * kSubBytes, s.v + off, kSubBytes, pp.full + stage);
+                    }
+                }
+            }
+        }
+    } else {
+        // ---- storer
+        if (lane == 0) {
+            int prev = -1;
+            for (int t = t0; t < t1; t++) {
+                if (*abort) break;
+                if (t >= s.end_tile || t < s.first_tile) load_seg<W>(s, c, prefix, t, me, me);
+                const int64_t base = (int64_t)(t - s.first_tile) * kTile;
+                const bool adam = ADAM && s.p != nullptr;
+                if (MODE == LOCAL && !adam) continue;
+                if (!(s.vec && s.n - base >= kTile)) continue;
+                for (int sub = 0; sub < kSubsPerTile; sub++, my_it++) {
+                    const int stage = my_it % pp.stages;
+                    if (!mbar_wait(pp.computed + stage, (my_it / pp.stages) & 1, a, c, abort)) break;
+                    const unsigned char* src = pp.data + (size_t)stage * pp.stage_bytes;
+                    const int64_t off = base + sub * kSub;
+                    if (MODE == REDUCE_PUSH) {
+#pragma unroll
+                        for (int r = 0; r < W; r++) bulk_store(s.g[r] + off, src, kSubBytes);  // r != me crosses NVLink
+                    }
+                    if (adam) {
+                        bulk_store(s.p + off, src + G * kSubBytes, kSubBytes);
+                        bulk_store(s.m + off, src + (G + 1) * kSubBytes, kSubBytes);
+                        bulk_store(s.v + off, src + (G + 2) * kSubBytes, kSubBytes);
+                    }
+                    bulk_commit();
+                    // a stage is free again once the stores that read it have done so: one step behind
+                    bulk_wait_read<1>();
+                    if (prev >= 0) mbar_arrive(pp.empty + prev);
+                    prev = stage;
+                }
+            }
+            bulk_wait_read<0>();
+            if (prev >= 0) mbar_arrive(pp.empty + prev);
+            bulk_wait_all();      // every byte this block wrote, locally or to a peer, has landed
+            fence_async_proxy();
+        }
+    }
+    it = my_it;
+    __syncwarp();
+    __syncthreads();
+}
+
+template <int W, bool ADAM>
+__global__ void __launch_bounds__(kPipeThreads, 2) k_step(const __grid_constant__ LaunchArgs a) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int G = a.blocks_per_rank;
+    const int b = blockIdx.x % G;
+    const RankCtx& c = a.ctxs[blockIdx.x / G];
+    const int me = c.rank, nseg = c.nseg;
+    Pipe pp;
+    pp.full = reinterpret_cast<uint64_t*>(smem);
+    pp.computed = pp.full + kMaxStages;
+    pp.empty = pp.full + 2 * kMaxStages;
+    pp.abort = reinterpret_cast<int*>(smem + 3 * kMaxStages * 8);
+    int* s_prefix = reinterpret_cast<int*>(smem + kPipeHeader);
+    pp.data = smem + kPipeHeader + ((((size_t)nseg + 1) * 4 + 127) & ~(size_t)127);
+    pp.stages = a.stages;
+    pp.stage_bytes = ((W > 1 ? W : 1) + (ADAM ? 3 : 0)) * kSubBytes;
+    for (int i = threadIdx.x; i <= nseg; i += kPipeThreads) s_prefix[i] = c.tile_prefix[i];
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kMaxStages; i++) {
+            mbar_init(pp.full + i, 1);
+            mbar_init(pp.computed + i, kThreads);
+            mbar_init(pp.empty + i, 1);
+        }
+        *pp.abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    const int T = s_prefix[nseg];
+    unsigned it = 0;
+
+    if (W == 1) {
+        pipe_run<W, ADAM, LOCAL>(a, c, pp, s_prefix, cut(T, b, G), cut(T, b + 1, G), me, it);
+        return;
+    }
+    post<W>(c, B_START, b, me, a.seq);
+    await<W>(c, a, B_START, b, me, -1, ST_TIMEOUT_START, pp.abort);
+    {   // own chunk: pull from every rank, reduce, update, push the mean to every rank
+        const int cb = cut(T, me, W), ce = cut(T, me + 1, W), L = ce - cb;
+        pipe_run<W, ADAM, REDUCE_PUSH>(a, c, pp, s_prefix, cb + cut(L, b, G), cb + cut(L, b + 1, G), me, it);
+    }
+    post<W>(c, B_REDUCED, b, me, a.seq);
+    if (ADAM) {
+        for (int k = 1; k < W; k++) {  // the other chunks arrive in the local gradient; update p, m, v from there
+            const int src = (me + k) % W;
+            await<W>(c, a, B_REDUCED, b, me, src, ST_TIMEOUT_REDUCED, pp.abort);
+            const int cb = cut(T, src, W), ce = cut(T, src + 1, W), L = ce - cb;
+            pipe_run<W, ADAM, LOCAL>(a, c, pp, s_prefix, cb + cut(L, b, G), cb + cut(L, b + 1, G), me, it);
+        }
+    } else {
+        // a bare all-reduce is complete here once every owner has written its chunk
+        await<W>(c, a, B_REDUCED, b, me, -1, ST_TIMEOUT_REDUCED, pp.abort);
+    }
+}
+
 // ---------------------------------------------------------------- small elementwise kernels next to the path
 
 // y = alpha * x (core/cuda/kernels.cu:208-212), y += alpha * x (sl_cuda_axpy), p = value (k_fill, :127-131).
@@ -446,21 +711,39 @@ __global__ void __launch_bounds__(kThreads) k_sumsq(int64_t n, const float* x, d
 // ---------------------------------------------------------------- launch
 
 template <int W, bool ADAM>
-static cudaError_t launch_w(bool oneshot, bool cooperative, int grid, size_t smem, const LaunchArgs& a, cudaStream_t st) {
-    void (*kern)(const LaunchArgs) = oneshot ? k_oneshot<W, ADAM> : k_twoshot<W, ADAM>;
+static void (*kernel_of(int kind))(const LaunchArgs) {
+    return kind == KERNEL_ONESHOT ? k_oneshot<W, ADAM> : kind == KERNEL_PLAIN ? k_twoshot<W, ADAM> : k_step<W, ADAM>;
+}
+
+template <int W, bool ADAM>
+static cudaError_t launch_w(int kind, bool cooperative, int grid, size_t smem, const LaunchArgs& a, cudaStream_t st) {
+    void (*kern)(const LaunchArgs) = kernel_of<W, ADAM>(kind);
+    const int threads = kind == KERNEL_STEP ? kPipeThreads : kThreads;
+    if (kind == KERNEL_STEP) {
+        static bool raised = false;  // per instantiation: allow more than 48 KiB of dynamic shared memory
+        if (!raised) {
+            const cudaError_t e = cudaFuncSetAttribute((const void*)kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kStepSmemMax);
+            if (e != cudaSuccess) return e;
+            raised = true;
+        }
+    }
     if (cooperative) {
         void* params[] = {const_cast<LaunchArgs*>(&a)};
-        return cudaLaunchCooperativeKernel((const void*)kern, dim3(grid), dim3(kThreads), params, smem, st);
+        return cudaLaunchCooperativeKernel((const void*)kern, dim3(grid), dim3(threads), params, smem, st);
     }
-    kern<<<grid, kThreads, smem, st>>>(a);
+    kern<<<grid, threads, smem, st>>>(a);
     return cudaPeekAtLastError();
 }
 
 template <int W, bool ADAM>
-static int occupancy_w(bool oneshot, size_t smem) {
+static int occupancy_w(int kind, size_t smem) {
     int n = 0;
-    void (*kern)(const LaunchArgs) = oneshot ? k_oneshot<W, ADAM> : k_twoshot<W, ADAM>;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, (const void*)kern, kThreads, smem) != cudaSuccess) return 0;
+    void (*kern)(const LaunchArgs) = kernel_of<W, ADAM>(kind);
+    if (kind == KERNEL_STEP &&
+        cudaFuncSetAttribute((const void*)kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kStepSmemMax) != cudaSuccess)
+        return 0;
+    const int threads = kind == KERNEL_STEP ? kPipeThreads : kThreads;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, (const void*)kern, threads, smem) != cudaSuccess) return 0;
     return n;
 }
 
@@ -476,15 +759,27 @@ static int occupancy_w(bool oneshot, size_t smem) {
         case 8: return adam ? fn<8, true>(__VA_ARGS__) : fn<8, false>(__VA_ARGS__); \
     }
 
-int launch_step(int world, bool adam, bool oneshot, bool cooperative, int grid, size_t smem, const LaunchArgs& a,
+int launch_step(int world, bool adam, int kind, bool cooperative, int grid, size_t smem, const LaunchArgs& a,
                 cudaStream_t st) {
-    SLB_DISPATCH(world, launch_w, oneshot, cooperative, grid, smem, a, st)
+    SLB_DISPATCH(world, launch_w, kind, cooperative, grid, smem, a, st)
     return (int)cudaErrorInvalidValue;
 }
 
-int step_occupancy(int world, bool adam, bool oneshot, size_t smem) {
-    SLB_DISPATCH(world, occupancy_w, oneshot, smem)
+int step_occupancy(int world, bool adam, int kind, size_t smem) {
+    SLB_DISPATCH(world, occupancy_w, kind, smem)
     return 0;
+}
+
+// Shared memory of k_step for a step of nseg segments: header, tile prefix, `stages` stages of one 4 KiB slot per
+// stream. Picks the deepest ring that keeps two blocks resident per SM. Returns 0 when even two stages do not fit.
+size_t step_smem(int world, bool adam, int nseg, int* stages) {
+    const size_t fixed = kPipeHeader + ((((size_t)nseg + 1) * 4 + 127) & ~(size_t)127);
+    const size_t stage = (size_t)((world > 1 ? world : 1) + (adam ? 3 : 0)) * kSubBytes;
+    int n = (int)((kStepSmemMax - fixed) / stage);
+    if (n > kMaxStages) n = kMaxStages;
+    if (n < 2) return 0;
+    *stages = n;
+    return fixed + n * stage;
 }
 
 static int flat_grid(int64_t n) {

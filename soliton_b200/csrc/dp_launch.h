@@ -8,13 +8,21 @@
 
 namespace slb {
 
-// Launches k_oneshot or k_twoshot for `world` ranks. `grid` = blocks_per_rank x (virtual ranks in this launch);
+enum KernelKind : int {
+    KERNEL_PLAIN = 0,    // k_twoshot: register-staged loads, pull-based all-gather (kept for comparison runs)
+    KERNEL_ONESHOT = 1,  // k_oneshot: small steps, push to staging + local reduce
+    KERNEL_STEP = 2,     // k_step: shared-memory ring fed by bulk async copies; the default for everything else
+};
+constexpr int kStepSmemMax = 110 * 1024;  // dynamic shared memory per block of k_step: two blocks fit one SM
+
+// Launches one kernel of the family for `world` ranks. `grid` = blocks_per_rank x (virtual ranks in this launch);
 // `cooperative` asks the driver to guarantee that all blocks are resident at once (required when several virtual
 // ranks, which wait on one another, share one GPU). Returns a cudaError_t value.
-int launch_step(int world, bool adam, bool oneshot, bool cooperative, int grid, size_t smem, const LaunchArgs& a,
+int launch_step(int world, bool adam, int kind, bool cooperative, int grid, size_t smem, const LaunchArgs& a,
                 cudaStream_t st);
 // Resident blocks per SM of that kernel variant.
-int step_occupancy(int world, bool adam, bool oneshot, size_t smem);
+int step_occupancy(int world, bool adam, int kind, size_t smem);
+size_t step_smem(int world, bool adam, int nseg, int* stages);
 
 int launch_scale(const float* x, float* y, int64_t n, float alpha, cudaStream_t st);
 int launch_axpy(const float* x, float* y, int64_t n, float alpha, cudaStream_t st);

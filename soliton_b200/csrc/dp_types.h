@@ -73,6 +73,7 @@ enum Status : int {
     ST_TIMEOUT_START = 21,   // a peer never announced its gradients
     ST_TIMEOUT_REDUCED = 22, // a peer never announced its reduced chunk / its staged gradients
     ST_TIMEOUT_DONE = 23,    // a peer never announced that it finished reading
+    ST_TIMEOUT_PIPE = 24,    // a bulk copy of this block's own shared-memory pipeline never completed
 };
 
 struct LaunchArgs {
@@ -83,6 +84,7 @@ struct LaunchArgs {
     int stage_slot_floats;          // capacity of one (parity, source rank) staging slot
     unsigned long long timeout_ns;  // bound of every flag wait
     float inv_world;
+    int stages;                     // shared-memory pipeline depth of k_step (2..8)
     Hyper hp[kMaxHyper];
 };
 

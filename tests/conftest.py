@@ -35,4 +35,5 @@ def cuda(lib):
     if lib.sl_cuda_count() < 1:
         pytest.fail("a test marked gpu ran without a CUDA device")
     T._dev(T.CUDA)
+    lib.slb_set_option(b"timeout_ms", 3000)  # a protocol bug should end a test in seconds, not hang it
     return T.CUDA
