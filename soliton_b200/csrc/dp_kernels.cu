@@ -33,7 +33,7 @@
 namespace slb {
 
 enum Mode : int { REDUCE_OWN = 0, GATHER = 1, PUSH = 2, REDUCE_STAGED = 3, REDUCE_PUSH = 4, LOCAL = 5 };
-enum Barrier : int { B_START = 0, B_REDUCED = 1, B_DONE = 2 };
+enum Barrier : int { B_START = 0, B_REDUCED = 1, B_DONE = 2, B_SLICE = 3 };  // rows of the flag area; B_SLICE + j
 
 // ---------------------------------------------------------------- memory primitives
 
@@ -497,124 +497,188 @@ __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wa
 __device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_proxy_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-// One run of tiles [t0, t1) through the pipeline. MODE REDUCE_PUSH: pull the tile from every rank, mean in rank
-// order, update own p/m/v, write the mean to every rank's gradient. MODE LOCAL: gradient already final in local
-// memory, update p/m/v. `it` counts pipeline steps over the whole kernel (stage index and mbarrier parity).
-template <int W, bool ADAM, int MODE>
-__device__ __forceinline__ void pipe_run(const LaunchArgs& a, const RankCtx& c, const Pipe& pp, const int* prefix, int t0,
-                                         int t1, int me, unsigned& it) {
-    constexpr int G = MODE == REDUCE_PUSH ? W : 1;  // gradient streams ahead of p, m, v in a stage
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    volatile int* abort = pp.abort;
+// What the three roles share while they walk the same list of work items. An item is a range of tiles in one
+// mode: REDUCE_PUSH (pull the tiles from every rank, mean in rank order, update own p/m/v, write the mean into
+// every rank's gradient) or LOCAL (the gradient in local memory is final: update p/m/v).
+template <int W>
+struct Walk {
+    const LaunchArgs& a;
+    const RankCtx& c;
+    const Pipe& pp;
+    const int* prefix;
+    int me, block;
+    unsigned it;      // pipeline steps so far: stage index and mbarrier parity; equal in all roles at item borders
+    int prev;         // storer: stage whose stores were issued last and that is not yet handed back
     SegView<W> s;
-    s.first_tile = 0, s.end_tile = 0;
-    unsigned my_it = it;  // every role walks the same tiles in the same order, so the counters stay equal
+    __device__ Walk(const LaunchArgs& a_, const RankCtx& c_, const Pipe& pp_, const int* prefix_, int me_, int block_)
+        : a(a_), c(c_), pp(pp_), prefix(prefix_), me(me_), block(block_), it(0), prev(-1) {
+        s.first_tile = 0, s.end_tile = 0;
+    }
+    __device__ __forceinline__ volatile int* abort() const { return pp.abort; }
+    // Positions the segment view on tile t; true when the tile goes through the ring in this mode.
+    template <bool ADAM, int MODE>
+    __device__ __forceinline__ bool ring_tile(int t, int64_t* base, bool* adam) {
+        if (t >= s.end_tile || t < s.first_tile) load_seg<W>(s, c, prefix, t, me, me);
+        *base = (int64_t)(t - s.first_tile) * kTile;
+        *adam = ADAM && s.p != nullptr;
+        if (MODE == LOCAL && !*adam) return false;
+        return s.vec && s.n - *base >= kTile;
+    }
+};
 
-    if (warp < kThreads / 32) {
-        // ---- compute warps
-        for (int t = t0; t < t1; t++) {
-            if (*abort) break;
-            if (t >= s.end_tile || t < s.first_tile) load_seg<W>(s, c, prefix, t, me, me);
-            const int64_t base = (int64_t)(t - s.first_tile) * kTile;
-            const bool adam = ADAM && s.p != nullptr;
-            if (MODE == LOCAL && !adam) continue;
-            if (!(s.vec && s.n - base >= kTile)) {
-                do_tile<W, ADAM, MODE>(s, a, c, t, me, nullptr, 0);
-                continue;
+// Tiles of [t0, t1) that cannot take the ring (ragged ends, unaligned tensors): plain accesses by the compute warps.
+template <int W, bool ADAM, int MODE>
+__device__ __forceinline__ void ragged_pass(Walk<W>& w, int t0, int t1) {
+    if (threadIdx.x >= kThreads) return;
+    for (int t = t0; t < t1; t++) {
+        int64_t base;
+        bool adam;
+        if (w.template ring_tile<ADAM, MODE>(t, &base, &adam)) continue;
+        if (MODE == LOCAL && !adam) continue;
+        do_tile<W, ADAM, MODE>(w.s, w.a, w.c, t, w.me, nullptr, 0);
+    }
+}
+
+// ---- loader: one thread. wait_src >= 0: the tiles were written by that rank; wait (bounded) for its flag first.
+template <int W, bool ADAM, int MODE>
+__device__ __forceinline__ void load_item(Walk<W>& w, int t0, int t1, int wait_src, int wait_row) {
+    constexpr int G = MODE == REDUCE_PUSH ? W : 1;
+    const Pipe& pp = w.pp;
+    if (*w.abort()) return;
+    if (wait_src >= 0) {
+        const unsigned* f = w.c.flags[w.me] + flag_index(wait_row, w.block, wait_src);
+        const unsigned long long start = global_ns();
+        while ((int)(ld_acquire_sys(f) - w.a.seq) < 0) {
+            if (global_ns() - start > w.a.timeout_ns) {
+                atomicCAS(w.c.status, 0, ST_TIMEOUT_REDUCED);
+                *w.abort() = 1;
+                return;
             }
-            const Hyper& h = a.hp[s.hyper];
-            for (int sub = 0; sub < kSubsPerTile; sub++, my_it++) {
-                const int stage = my_it % pp.stages;
-                if (!mbar_wait(pp.full + stage, (my_it / pp.stages) & 1, a, c, abort)) break;
-                float4* st = reinterpret_cast<float4*>(pp.data + (size_t)stage * pp.stage_bytes) + threadIdx.x;
-                float4 avg = st[0];
-                if (MODE == REDUCE_PUSH) {
-#pragma unroll
-                    for (int r = 1; r < W; r++) avg = add4(avg, st[r * kThreads]);
-                    avg = mul4(avg, a.inv_world);
-                    st[0] = avg;
-                }
-                if (adam) {
-                    float4 p = st[G * kThreads], m = st[(G + 1) * kThreads], v = st[(G + 2) * kThreads];
-                    adamw_vec(p, avg, m, v, h, s.wd);
-                    st[G * kThreads] = p, st[(G + 1) * kThreads] = m, st[(G + 2) * kThreads] = v;
-                }
-                fence_async_proxy_smem();  // the bulk stores read what was just written through the generic proxy
-                mbar_arrive(pp.computed + stage);
-            }
-        }
-    } else if (warp == kThreads / 32) {
-        // ---- loader
-        if (lane == 0) {
-            fence_async_proxy();  // peers' gradients were observed through flags by generic loads; bulk loads follow
-            for (int t = t0; t < t1; t++) {
-                if (*abort) break;
-                if (t >= s.end_tile || t < s.first_tile) load_seg<W>(s, c, prefix, t, me, me);
-                const int64_t base = (int64_t)(t - s.first_tile) * kTile;
-                const bool adam = ADAM && s.p != nullptr;
-                if (MODE == LOCAL && !adam) continue;
-                if (!(s.vec && s.n - base >= kTile)) continue;
-                for (int sub = 0; sub < kSubsPerTile; sub++, my_it++) {
-                    const int stage = my_it % pp.stages;
-                    if (!mbar_wait(pp.empty + stage, ((my_it / pp.stages) & 1) ^ 1, a, c, abort)) break;
-                    unsigned char* dst = pp.data + (size_t)stage * pp.stage_bytes;
-                    const int64_t off = base + sub * kSub;
-                    mbar_arrive_expect(pp.full + stage, (unsigned)((G + (adam ? 3 : 0)) * kSubBytes));
-                    if (MODE == REDUCE_PUSH) {
-#pragma unroll
-                        for (int r = 0; r < W; r++) bulk_load(dst + r * kSubBytes, s.g[r] + off, kSubBytes, pp.full + stage);
-                    } else {
-                        bulk_load(dst, s.gme + off, kSubBytes, pp.full + stage);
-                    }
-                    if (adam) {
-                        bulk_load(dst + G * kSubBytes, s.p + off, kSubBytes, pp.full + stage);
-                        bulk_load(dst + (G + 1) * kSubBytes, s.m + off, kSubBytes, pp.full + stage);
-                        bulk_load(dst + (G + 2) * kSubBytes, s.v + off, kSubBytes, pp.full + stage);
-                    }
-                }
-            }
-        }
-    } else {
-        // ---- storer
-        if (lane == 0) {
-            int prev = -1;
-            for (int t = t0; t < t1; t++) {
-                if (*abort) break;
-                if (t >= s.end_tile || t < s.first_tile) load_seg<W>(s, c, prefix, t, me, me);
-                const int64_t base = (int64_t)(t - s.first_tile) * kTile;
-                const bool adam = ADAM && s.p != nullptr;
-                if (MODE == LOCAL && !adam) continue;
-                if (!(s.vec && s.n - base >= kTile)) continue;
-                for (int sub = 0; sub < kSubsPerTile; sub++, my_it++) {
-                    const int stage = my_it % pp.stages;
-                    if (!mbar_wait(pp.computed + stage, (my_it / pp.stages) & 1, a, c, abort)) break;
-                    const unsigned char* src = pp.data + (size_t)stage * pp.stage_bytes;
-                    const int64_t off = base + sub * kSub;
-                    if (MODE == REDUCE_PUSH) {
-#pragma unroll
-                        for (int r = 0; r < W; r++) bulk_store(s.g[r] + off, src, kSubBytes);  // r != me crosses NVLink
-                    }
-                    if (adam) {
-                        bulk_store(s.p + off, src + G * kSubBytes, kSubBytes);
-                        bulk_store(s.m + off, src + (G + 1) * kSubBytes, kSubBytes);
-                        bulk_store(s.v + off, src + (G + 2) * kSubBytes, kSubBytes);
-                    }
-                    bulk_commit();
-                    // a stage is free again once the stores that read it have done so: one step behind
-                    bulk_wait_read<1>();
-                    if (prev >= 0) mbar_arrive(pp.empty + prev);
-                    prev = stage;
-                }
-            }
-            bulk_wait_read<0>();
-            if (prev >= 0) mbar_arrive(pp.empty + prev);
-            bulk_wait_all();      // every byte this block wrote, locally or to a peer, has landed
-            fence_async_proxy();
+            __nanosleep(32);
         }
     }
-    it = my_it;
-    __syncwarp();
-    __syncthreads();
+    fence_async_proxy();  // what generic-proxy flags made visible is read by the bulk-copy engine from here on
+    for (int t = t0; t < t1; t++) {
+        if (*w.abort()) return;
+        int64_t base;
+        bool adam;
+        if (!w.template ring_tile<ADAM, MODE>(t, &base, &adam)) continue;
+        for (int sub = 0; sub < kSubsPerTile; sub++, w.it++) {
+            const int stage = w.it % pp.stages;
+            if (!mbar_wait(pp.empty + stage, ((w.it / pp.stages) & 1) ^ 1, w.a, w.c, w.abort())) return;
+            unsigned char* dst = pp.data + (size_t)stage * pp.stage_bytes;
+            const int64_t off = base + sub * kSub;
+            mbar_arrive_expect(pp.full + stage, (unsigned)((G + (adam ? 3 : 0)) * kSubBytes));
+            if (MODE == REDUCE_PUSH) {
+#pragma unroll
+                for (int r = 0; r < W; r++) bulk_load(dst + r * kSubBytes, w.s.g[r] + off, kSubBytes, pp.full + stage);
+            } else {
+                bulk_load(dst, w.s.gme + off, kSubBytes, pp.full + stage);
+            }
+            if (adam) {
+                bulk_load(dst + G * kSubBytes, w.s.p + off, kSubBytes, pp.full + stage);
+                bulk_load(dst + (G + 1) * kSubBytes, w.s.m + off, kSubBytes, pp.full + stage);
+                bulk_load(dst + (G + 2) * kSubBytes, w.s.v + off, kSubBytes, pp.full + stage);
+            }
+        }
+    }
+}
+
+// ---- compute warps: 256 threads, one float4 of every stream each, in place in shared memory.
+template <int W, bool ADAM, int MODE>
+__device__ __forceinline__ void compute_item(Walk<W>& w, int t0, int t1) {
+    constexpr int G = MODE == REDUCE_PUSH ? W : 1;
+    const Pipe& pp = w.pp;
+    for (int t = t0; t < t1; t++) {
+        if (*w.abort()) return;
+        int64_t base;
+        bool adam;
+        if (!w.template ring_tile<ADAM, MODE>(t, &base, &adam)) continue;
+        const Hyper& h = w.a.hp[w.s.hyper];
+        for (int sub = 0; sub < kSubsPerTile; sub++, w.it++) {
+            const int stage = w.it % pp.stages;
+            if (!mbar_wait(pp.full + stage, (w.it / pp.stages) & 1, w.a, w.c, w.abort())) return;
+            float4* st = reinterpret_cast<float4*>(pp.data + (size_t)stage * pp.stage_bytes) + threadIdx.x;
+            float4 avg = st[0];
+            if (MODE == REDUCE_PUSH) {
+#pragma unroll
+                for (int r = 1; r < W; r++) avg = add4(avg, st[r * kThreads]);
+                avg = mul4(avg, w.a.inv_world);
+                st[0] = avg;
+            }
+            if (adam) {
+                float4 p = st[G * kThreads], m = st[(G + 1) * kThreads], v = st[(G + 2) * kThreads];
+                adamw_vec(p, avg, m, v, h, w.s.wd);
+                st[G * kThreads] = p, st[(G + 1) * kThreads] = m, st[(G + 2) * kThreads] = v;
+            }
+            fence_async_proxy_smem();  // the bulk stores read what was just written through the generic proxy
+            mbar_arrive(pp.computed + stage);
+        }
+    }
+}
+
+// ---- storer: one thread. post_row >= 0: once every store of the item has landed, publish the flag to all peers.
+template <int W, bool ADAM, int MODE>
+__device__ __forceinline__ void store_item(Walk<W>& w, int t0, int t1, int post_row) {
+    constexpr int G = MODE == REDUCE_PUSH ? W : 1;
+    const Pipe& pp = w.pp;
+    for (int t = t0; t < t1; t++) {
+        if (*w.abort()) break;
+        int64_t base;
+        bool adam;
+        if (!w.template ring_tile<ADAM, MODE>(t, &base, &adam)) continue;
+        for (int sub = 0; sub < kSubsPerTile; sub++, w.it++) {
+            const int stage = w.it % pp.stages;
+            if (!mbar_wait(pp.computed + stage, (w.it / pp.stages) & 1, w.a, w.c, w.abort())) break;
+            const unsigned char* src = pp.data + (size_t)stage * pp.stage_bytes;
+            const int64_t off = base + sub * kSub;
+            if (MODE == REDUCE_PUSH) {
+#pragma unroll
+                for (int r = 0; r < W; r++) bulk_store(w.s.g[r] + off, src, kSubBytes);  // r != me crosses NVLink
+            }
+            if (adam) {
+                bulk_store(w.s.p + off, src + G * kSubBytes, kSubBytes);
+                bulk_store(w.s.m + off, src + (G + 1) * kSubBytes, kSubBytes);
+                bulk_store(w.s.v + off, src + (G + 2) * kSubBytes, kSubBytes);
+            }
+            bulk_commit();
+            bulk_wait_read<1>();  // all but the newest group have read their stage: the previous one is free again
+            if (w.prev >= 0) mbar_arrive(pp.empty + w.prev);
+            w.prev = stage;
+        }
+    }
+    if (post_row >= 0) {
+        bulk_wait_read<0>();
+        if (w.prev >= 0) mbar_arrive(pp.empty + w.prev);
+        w.prev = -1;
+        bulk_wait_all();  // every byte of the item, local or on a peer, has landed
+        fence_async_proxy();
+        __threadfence_system();
+#pragma unroll
+        for (int r = 0; r < W; r++)
+            if (r != w.me) st_release_sys(w.c.flags[r] + flag_index(post_row, w.block, w.me), w.a.seq);
+    }
+}
+
+// storer, end of kernel: hand back the last stage and wait for the last stores
+template <int W>
+__device__ __forceinline__ void store_drain(Walk<W>& w) {
+    bulk_wait_read<0>();
+    if (w.prev >= 0) mbar_arrive(w.pp.empty + w.prev);
+    w.prev = -1;
+    bulk_wait_all();
+    fence_async_proxy();
+}
+
+// One item, whichever role the calling thread has.
+template <int W, bool ADAM, int MODE>
+__device__ __forceinline__ void run_item(Walk<W>& w, int role, int t0, int t1, int wait_src, int wait_row, int post_row) {
+    if (role == 0)
+        compute_item<W, ADAM, MODE>(w, t0, t1);
+    else if (role == 1)
+        load_item<W, ADAM, MODE>(w, t0, t1, wait_src, wait_row);
+    else if (role == 2)
+        store_item<W, ADAM, MODE>(w, t0, t1, post_row);
 }
 
 template <int W, bool ADAM>
@@ -645,29 +709,64 @@ __global__ void __launch_bounds__(kPipeThreads, 2) k_step(const __grid_constant_
     }
     __syncthreads();
     const int T = s_prefix[nseg];
-    unsigned it = 0;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // 0: compute (warps 0-7), 1: loader (warp 8, lane 0), 2: storer (warp 9, lane 0), 3: idle lanes of warps 8-9
+    const int role = warp < kThreads / 32 ? 0 : (lane != 0 ? 3 : (warp == kThreads / 32 ? 1 : 2));
+    Walk<W> w(a, c, pp, s_prefix, me, b);
 
     if (W == 1) {
-        pipe_run<W, ADAM, LOCAL>(a, c, pp, s_prefix, cut(T, b, G), cut(T, b + 1, G), me, it);
+        const int t0 = cut(T, b, G), t1 = cut(T, b + 1, G);
+        ragged_pass<W, ADAM, LOCAL>(w, t0, t1);
+        run_item<W, ADAM, LOCAL>(w, role, t0, t1, -1, 0, -1);
+        if (role == 2) store_drain<W>(w);
         return;
     }
+
+    // The run of block b inside chunk ch, and slice j of that run.
+    auto run_of = [&](int ch, int* r0, int* r1) {
+        const int cb = cut(T, ch, W), L = cut(T, ch + 1, W) - cb;
+        *r0 = cb + cut(L, b, G), *r1 = cb + cut(L, b + 1, G);
+    };
+    int own0, own1;
+    run_of(me, &own0, &own1);
+
     post<W>(c, B_START, b, me, a.seq);
     await<W>(c, a, B_START, b, me, -1, ST_TIMEOUT_START, pp.abort);
-    {   // own chunk: pull from every rank, reduce, update, push the mean to every rank
-        const int cb = cut(T, me, W), ce = cut(T, me + 1, W), L = ce - cb;
-        pipe_run<W, ADAM, REDUCE_PUSH>(a, c, pp, s_prefix, cb + cut(L, b, G), cb + cut(L, b + 1, G), me, it);
-    }
+    // ragged tiles of the own chunk first, published through the block-wide barrier row
+    if (!*pp.abort) ragged_pass<W, ADAM, REDUCE_PUSH>(w, own0, own1);
     post<W>(c, B_REDUCED, b, me, a.seq);
-    if (ADAM) {
-        for (int k = 1; k < W; k++) {  // the other chunks arrive in the local gradient; update p, m, v from there
-            const int src = (me + k) % W;
-            await<W>(c, a, B_REDUCED, b, me, src, ST_TIMEOUT_REDUCED, pp.abort);
-            const int cb = cut(T, src, W), ce = cut(T, src + 1, W), L = ce - cb;
-            pipe_run<W, ADAM, LOCAL>(a, c, pp, s_prefix, cb + cut(L, b, G), cb + cut(L, b + 1, G), me, it);
+
+    // Whole tiles: the own chunk slice by slice, each slice's mean published as soon as its stores have landed;
+    // one slice behind, the same slice of every other chunk is picked up from local memory. Pulls over NVLink and
+    // the purely local updates therefore overlap instead of following one another.
+    for (int j = 0; j <= kSlices; j++) {
+        if (j < kSlices) {
+            const int len = own1 - own0;
+            run_item<W, ADAM, REDUCE_PUSH>(w, role, own0 + cut(len, j, kSlices), own0 + cut(len, j + 1, kSlices), -1, 0,
+                                           B_SLICE + j);
         }
-    } else {
-        // a bare all-reduce is complete here once every owner has written its chunk
-        await<W>(c, a, B_REDUCED, b, me, -1, ST_TIMEOUT_REDUCED, pp.abort);
+        if (j >= 1) {
+            for (int k = 1; k < W; k++) {
+                const int src = (me + k) % W;
+                int r0, r1;
+                run_of(src, &r0, &r1);
+                const int len = r1 - r0;
+                // without an optimizer the item moves nothing; the loader still waits, so that the kernel only ends
+                // once every owner has written its slices into this rank's gradient
+                run_item<W, ADAM, LOCAL>(w, role, r0 + cut(len, j - 1, kSlices), r0 + cut(len, j, kSlices), src,
+                                         B_SLICE + j - 1, -1);
+            }
+        }
+    }
+    if (role == 2) store_drain<W>(w);
+    __syncwarp();
+    await<W>(c, a, B_REDUCED, b, me, -1, ST_TIMEOUT_REDUCED, pp.abort);  // the peers' ragged tiles have arrived
+    if (ADAM && !*pp.abort) {
+        for (int k = 1; k < W; k++) {
+            int r0, r1;
+            run_of((me + k) % W, &r0, &r1);
+            ragged_pass<W, ADAM, LOCAL>(w, r0, r1);
+        }
     }
 }
 

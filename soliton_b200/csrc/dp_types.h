@@ -17,7 +17,9 @@ constexpr int kVecPerThread = 2;    // float4 vectors per thread, tensor stream 
 constexpr int kTile = 4 * kThreads * kVecPerThread;  // floats per tile: 2048 (8 KiB per tensor stream)
 constexpr int kMaxSegs = 4096;      // segments per step
 constexpr int kMaxHyper = 8;        // distinct hyperparameter sets per step
-constexpr int kFlagBlocks = 2048;   // upper bound on blocks per rank that take part in flag barriers
+constexpr int kFlagBlocks = 1024;   // upper bound on blocks per rank that take part in flag barriers
+constexpr int kSlices = 8;          // pieces a block's run of a chunk is cut into; the mean is published per piece
+constexpr int kFlagRows = 3 + kSlices;  // start, reduced, done, then one row per slice
 
 // Workspace the path reserves once per device from the deterministic allocator (identically on meta):
 // [control: rank contexts, flag words, segment table, tile prefix][one-shot staging].
@@ -26,8 +28,8 @@ constexpr size_t kStageBytes = size_t(16) << 20;
 constexpr size_t kWorkspaceBytes = kCtlBytes + kStageBytes;  // 18 MiB
 // Offsets inside the control area.
 constexpr size_t kCtxOff = 0;                                   // kMaxWorld rank contexts (emulation uses all)
-constexpr size_t kFlagOff = 8192;                               // 3 barriers x kFlagBlocks x kMaxWorld x 4 B
-constexpr size_t kFlagBytes = size_t(3) * kFlagBlocks * kMaxWorld * 4;
+constexpr size_t kFlagOff = 8192;                               // kFlagRows x kFlagBlocks x kMaxWorld x 4 B
+constexpr size_t kFlagBytes = size_t(kFlagRows) * kFlagBlocks * kMaxWorld * 4;
 constexpr size_t kTilePrefixOff = kFlagOff + kFlagBytes;        // (kMaxSegs + 1) ints
 constexpr size_t kSegOff = kTilePrefixOff + 32768;              // kMaxSegs segments
 constexpr size_t kPartialOff = kSegOff + size_t(kMaxSegs) * 112;  // kSumsqBlocks doubles (sum-of-squares partials)
