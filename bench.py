@@ -47,7 +47,7 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--mode", type=int, default=0, help="0 auto, 1 one-shot, 2 two-shot")
     ap.add_argument("--blocks-per-sm", type=int, default=0)
-    ap.add_argument("--pipeline", type=int, default=1, help="0: plain register-staged kernel (comparison only)")
+    ap.add_argument("--pipeline", type=int, default=-1, help="-1 auto, 1 k_step (shared-memory ring), 0 k_twoshot")
     return ap.parse_args()
 
 
@@ -185,8 +185,8 @@ def run_ours(args, rank, local_rank, world):
         set_option("mode", args.mode)
     if args.blocks_per_sm:
         set_option("blocks_per_sm", args.blocks_per_sm)
-    if not args.pipeline:
-        set_option("pipeline", 0)
+    if args.pipeline >= 0:
+        set_option("pipeline", args.pipeline)
     if world > 1:
         idt = torch.zeros(128, dtype=torch.uint8, device="cuda")
         if rank == 0:
@@ -280,7 +280,8 @@ def run_ours(args, rank, local_rank, world):
     nvl_bytes = 8.0 * P * (world - 1) / world
     t_nvl = nvl_bytes / (NVLINK_GBS * 1e9)
     per_launch_ms = total_ms / max(launches, 1)
-    base = "k_step" if args.pipeline else "k_twoshot"
+    use_step = args.pipeline == 1 or (args.pipeline < 0 and world == 2)
+    base = "k_step" if use_step else "k_twoshot"
     kernel = {0: f"{base}<1,adam>", 1: f"k_oneshot<{world},adam>", 2: f"{base}<{world},adam>"}[mode]
     traffic = NCU_DRAM_BYTES_PER_PARAM.get(world)
     if t_hbm >= t_nvl:

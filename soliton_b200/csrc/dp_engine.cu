@@ -273,6 +273,15 @@ static int stage_slot_floats(int world) {
     return (int)(raw / kTile * kTile);
 }
 
+// The kernel for steps too large for one-shot. Both candidates compute the same bits; the choice is by measured
+// time on 8xB200 with the GPT-2 124M parameter set: at two ranks, where HBM and NVLink bind together, the
+// shared-memory ring (k_step) is ahead; at one rank and from four ranks on, where the NVLink round trips of both
+// directions carry the load, the register-staged kernel (k_twoshot) is.
+static int large_step_kernel(int option, int world) {
+    if (option >= 0) return option ? KERNEL_STEP : KERNEL_PLAIN;
+    return world == 2 ? KERNEL_STEP : KERNEL_PLAIN;
+}
+
 static int min_chunk(int T, int world) {
     int best = T;
     for (int c = 0; c < world; c++) {
@@ -299,9 +308,7 @@ int Engine::launch_items(std::vector<StepItem>& items, const std::vector<HyperKe
         const bool small = opt.oneshot_max_bytes < 0 || T * kTile * 4 <= opt.oneshot_max_bytes;
         oneshot = fits && (opt.mode == 1 || (opt.mode == 0 && small));
     }
-    // Which kernel: the one-shot for small collectives, the shared-memory pipeline for everything else (the plain
-    // register-staged kernel only when asked for, as the yardstick the pipeline is measured against).
-    const int kind = oneshot ? KERNEL_ONESHOT : (opt.pipeline ? KERNEL_STEP : KERNEL_PLAIN);
+    const int kind = oneshot ? KERNEL_ONESHOT : large_step_kernel(opt.pipeline, W);
     int stages = 0;
     const size_t smem = kind == KERNEL_STEP ? step_smem(W, adam, nseg, &stages) : (size_t)(nseg + 1) * sizeof(int);
     if (smem == 0) return ERR_LAUNCH;
@@ -635,7 +642,7 @@ int Engine::sim_step(int world, int nseg, const int64_t* n, float* const* p, flo
     const bool fits = T * kTile <= slot_floats;
     bool oneshot = world > 1 && fits && (mode == 1 || (mode == 0 && T * kTile * 4 <= (opt.oneshot_max_bytes < 0 ? INT64_MAX : opt.oneshot_max_bytes)));
     if (mode == 1 && !oneshot) return -4;  // asked for one-shot, but the step does not fit the staging slots
-    const int kind = oneshot ? KERNEL_ONESHOT : (opt.pipeline ? KERNEL_STEP : KERNEL_PLAIN);
+    const int kind = oneshot ? KERNEL_ONESHOT : large_step_kernel(opt.pipeline, world);
     int stages = 0;
     const size_t smem = kind == KERNEL_STEP ? step_smem(world, adam != 0, nseg, &stages) : (size_t)(nseg + 1) * sizeof(int);
     if (smem == 0) return -3;

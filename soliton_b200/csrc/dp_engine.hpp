@@ -24,7 +24,8 @@ struct Options {
     int eager = 0;                          // 1: launch at every call instead of deferring (debugging aid)
     int mode = 0;                           // 0: pick one-shot / two-shot by size; 1: one-shot; 2: two-shot
     int blocks_per_sm = 0;                  // 0: as many as are resident
-    int pipeline = 1;                       // 1: k_step (shared-memory pipeline); 0: the plain register-staged kernel
+    int pipeline = -1;                      // which large-step kernel: 1 k_step (shared-memory ring), 0 k_twoshot
+                                            // (register-staged), -1 the faster of the two as measured per world size
     unsigned long long timeout_ns = 10ull * 1000 * 1000 * 1000;  // bound of every device-side flag wait
     double host_timeout_s = 120.0;          // bound of every host-side wait on a peer
     long long oneshot_max_bytes = -1;       // -1: whatever fits the staging slots

@@ -32,7 +32,7 @@
 
 namespace slb {
 
-enum Mode : int { REDUCE_OWN = 0, GATHER = 1, PUSH = 2, REDUCE_STAGED = 3, REDUCE_PUSH = 4, LOCAL = 5 };
+enum Mode : int { REDUCE_OWN = 0, GATHER = 1, PUSH = 2, REDUCE_STAGED = 3 };
 enum Barrier : int { B_START = 0, B_REDUCED = 1, B_DONE = 2, B_SLICE = 3 };  // rows of the flag area; B_SLICE + j
 
 // ---------------------------------------------------------------- memory primitives
@@ -199,10 +199,8 @@ __device__ __forceinline__ void do_tile(const SegView<W>& s, const LaunchArgs& a
     const Hyper& h = a.hp[s.hyper];
     const bool adam = ADAM && s.p != nullptr;
     constexpr int U = kTile / (4 * kThreads);
-    // REDUCE_PUSH and LOCAL only ever see the tiles the pipelined kernel leaves to this routine (partial or unaligned)
-    constexpr bool kScalarOnly = MODE == REDUCE_PUSH || MODE == LOCAL;
 
-    if (!kScalarOnly && s.vec && cnt == kTile) {
+    if (s.vec && cnt == kTile) {
         float4 gv[U][W], pv[U], mv[U], vv[U];
         // every load of the tile is issued before the first use
 #pragma unroll
@@ -271,15 +269,13 @@ __device__ __forceinline__ void do_tile(const SegView<W>& s, const LaunchArgs& a
             float avg;
             if (MODE == GATHER) {
                 avg = ld_sys1(s.gsrc + off);
-            } else if (MODE == LOCAL) {
-                avg = ld_sys1(s.gme + off);  // the owner of this chunk pushed the mean here during this launch
             } else if (W == 1) {
                 avg = s.gme[off];
             } else {
                 float x[W];
 #pragma unroll
                 for (int r = 0; r < W; r++) {
-                    if (MODE == REDUCE_OWN || MODE == REDUCE_PUSH)
+                    if (MODE == REDUCE_OWN)
                         x[r] = ld_sys1(s.g[r] + off);
                     else
                         x[r] = r == me ? ld_sys1(s.gme + off) : ld_sys1(stage + (size_t)r * slot + (size_t)t * kTile + e);
@@ -289,16 +285,68 @@ __device__ __forceinline__ void do_tile(const SegView<W>& s, const LaunchArgs& a
                 for (int r = 1; r < W; r++) avg = __fadd_rn(avg, x[r]);
                 avg = __fmul_rn(avg, a.inv_world);
             }
-            if (MODE == REDUCE_PUSH) {
-#pragma unroll
-                for (int r = 0; r < W; r++) s.g[r][off] = avg;  // the mean goes to every rank's gradient
-            } else if (W > 1 && MODE != LOCAL) {
-                s.gme[off] = avg;
-            }
+            if (W > 1) s.gme[off] = avg;
             if (adam) {
                 float p = s.p[off], m = s.m[off], v = s.v[off];
                 adamw_elem(p, avg, m, v, h, s.wd);
                 s.p[off] = p, s.m[off] = m, s.v[off] = v;
+            }
+        }
+    }
+}
+
+// Several whole tiles of one segment at once (k_twoshot only): every peer load of the group is issued before the
+// first tile is touched, so that a thread has kGroup x 2 x (streams) 16-byte NVLink loads outstanding instead of
+// 2 x (streams). The all-gather half of the exchange has a single remote stream and needs that depth to cover
+// the NVLink round trip; the reduce half needs it at small world sizes.
+template <int W, int MODE>
+constexpr int kGroup = MODE == GATHER ? 4 : (W >= 5 ? 1 : (W >= 3 ? 2 : 4));
+
+template <int W, bool ADAM, int MODE>
+__device__ __forceinline__ void do_group(const SegView<W>& s, const LaunchArgs& a, int t, int me) {
+    constexpr int U = kTile / (4 * kThreads), GR = kGroup<W, MODE>, NS = MODE == GATHER ? 1 : W;
+    const int tid = threadIdx.x;
+    const int64_t base = (int64_t)(t - s.first_tile) * kTile;
+    const Hyper& h = a.hp[s.hyper];
+    const bool adam = ADAM && s.p != nullptr;
+    float4 gv[GR][U][NS];
+#pragma unroll
+    for (int k = 0; k < GR; k++)
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const int64_t off = base + (int64_t)k * kTile + (tid + u * kThreads) * 4;
+            if (MODE == GATHER) {
+                gv[k][u][0] = ld_sys4(s.gsrc + off);
+            } else {
+#pragma unroll
+                for (int r = 0; r < W; r++) gv[k][u][r] = ld_sys4(s.g[r] + off);
+            }
+        }
+#pragma unroll
+    for (int k = 0; k < GR; k++) {
+        float4 pv[U], mv[U], vv[U];
+        if (adam) {
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                const int64_t off = base + (int64_t)k * kTile + (tid + u * kThreads) * 4;
+                pv[u] = ld_stream4(s.p + off), mv[u] = ld_stream4(s.m + off), vv[u] = ld_stream4(s.v + off);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const int64_t off = base + (int64_t)k * kTile + (tid + u * kThreads) * 4;
+            float4 avg = gv[k][u][0];
+            if (MODE != GATHER) {
+#pragma unroll
+                for (int r = 1; r < W; r++) avg = add4(avg, gv[k][u][r]);
+                avg = mul4(avg, a.inv_world);
+            }
+            st_stream4(s.gme + off, avg);
+            if (adam) {
+                adamw_vec(pv[u], avg, mv[u], vv[u], h, s.wd);
+                st_stream4(s.p + off, pv[u]);
+                st_stream4(s.m + off, mv[u]);
+                st_stream4(s.v + off, vv[u]);
             }
         }
     }
@@ -311,6 +359,15 @@ __device__ __forceinline__ void do_run(const LaunchArgs& a, const RankCtx& c, co
     s.first_tile = 0, s.end_tile = 0;
     for (int t = t0; t < t1; t++) {
         if (t >= s.end_tile || t < s.first_tile) load_seg<W>(s, c, prefix, t, me, src);
+        if (W > 1 && (MODE == GATHER || MODE == REDUCE_OWN)) {
+            constexpr int GR = kGroup<W, (MODE == GATHER ? GATHER : REDUCE_OWN)>;
+            // the next GR tiles lie in this run, in this segment, and are whole and aligned
+            if (GR > 1 && s.vec && t + GR <= t1 && (int64_t)(t + GR - s.first_tile) * kTile <= s.n) {
+                do_group<W, ADAM, (MODE == GATHER ? GATHER : REDUCE_OWN)>(s, a, t, me);
+                t += GR - 1;
+                continue;
+            }
+        }
         do_tile<W, ADAM, MODE>(s, a, c, t, me, stage, stage_off);
     }
 }
@@ -498,55 +555,69 @@ __device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.
 __device__ __forceinline__ void fence_async_proxy_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // What the three roles share while they walk the same list of work items. An item is a range of tiles in one
-// mode: REDUCE_PUSH (pull the tiles from every rank, mean in rank order, update own p/m/v, write the mean into
-// every rank's gradient) or LOCAL (the gradient in local memory is final: update p/m/v).
+// mode: REDUCE_OWN (pull the tiles from every rank, mean in rank order, store it into the own gradient, update own
+// p/m/v) or GATHER (pull the finished mean from its owner `src`, store it into the local gradient, update p/m/v;
+// src == me, the single-rank step, reads the local gradient and stores no gradient).
+// A ring step of REDUCE_OWN covers one sub-tile (kSub floats) of W gradient streams plus p, m, v. A step of GATHER
+// has only four streams, so it covers as many sub-tiles as fit the same stage (`gsubs`, 1 or 2).
 template <int W>
 struct Walk {
     const LaunchArgs& a;
     const RankCtx& c;
     const Pipe& pp;
     const int* prefix;
-    int me, block;
-    unsigned it;      // pipeline steps so far: stage index and mbarrier parity; equal in all roles at item borders
-    int prev;         // storer: stage whose stores were issued last and that is not yet handed back
+    int me, block, src;
+    unsigned it;      // ring steps so far: stage index and mbarrier parity; equal in all roles at item borders
     SegView<W> s;
     __device__ Walk(const LaunchArgs& a_, const RankCtx& c_, const Pipe& pp_, const int* prefix_, int me_, int block_)
-        : a(a_), c(c_), pp(pp_), prefix(prefix_), me(me_), block(block_), it(0), prev(-1) {
+        : a(a_), c(c_), pp(pp_), prefix(prefix_), me(me_), block(block_), src(me_), it(0) {
         s.first_tile = 0, s.end_tile = 0;
     }
     __device__ __forceinline__ volatile int* abort() const { return pp.abort; }
-    // Positions the segment view on tile t; true when the tile goes through the ring in this mode.
-    template <bool ADAM, int MODE>
+    __device__ __forceinline__ void set_src(int src_) {
+        if (src_ != src) s.first_tile = 0, s.end_tile = 0;  // the view caches the owner's pointer
+        src = src_;
+    }
+    // Positions the segment view on tile t; true when the tile goes through the ring.
+    template <bool ADAM>
     __device__ __forceinline__ bool ring_tile(int t, int64_t* base, bool* adam) {
-        if (t >= s.end_tile || t < s.first_tile) load_seg<W>(s, c, prefix, t, me, me);
+        if (t >= s.end_tile || t < s.first_tile) load_seg<W>(s, c, prefix, t, me, src);
         *base = (int64_t)(t - s.first_tile) * kTile;
         *adam = ADAM && s.p != nullptr;
-        if (MODE == LOCAL && !*adam) return false;
         return s.vec && s.n - *base >= kTile;
     }
 };
 
+// Slots one gathered sub-tile takes in a stage (gradient, and p, m, v with an optimizer), and how many sub-tiles a
+// GATHER step covers: as many as fit the stage, which is sized for a REDUCE_OWN step of W + 3 (or W) slots.
+template <bool ADAM>
+constexpr int kGatherSlots = ADAM ? 4 : 1;
+template <int W, bool ADAM>
+constexpr int kGatherSubs =
+    ((W > 1 ? W : 1) + (ADAM ? 3 : 0)) / kGatherSlots<ADAM> >= kSubsPerTile ? kSubsPerTile : 1;
+
 // Tiles of [t0, t1) that cannot take the ring (ragged ends, unaligned tensors): plain accesses by the compute warps.
 template <int W, bool ADAM, int MODE>
-__device__ __forceinline__ void ragged_pass(Walk<W>& w, int t0, int t1) {
+__device__ __forceinline__ void ragged_pass(Walk<W>& w, int t0, int t1, int src) {
     if (threadIdx.x >= kThreads) return;
+    w.set_src(src);
     for (int t = t0; t < t1; t++) {
         int64_t base;
         bool adam;
-        if (w.template ring_tile<ADAM, MODE>(t, &base, &adam)) continue;
-        if (MODE == LOCAL && !adam) continue;
+        if (w.template ring_tile<ADAM>(t, &base, &adam)) continue;
         do_tile<W, ADAM, MODE>(w.s, w.a, w.c, t, w.me, nullptr, 0);
     }
 }
 
-// ---- loader: one thread. wait_src >= 0: the tiles were written by that rank; wait (bounded) for its flag first.
+// ---- loader: one thread. wait_row >= 0: the tiles are written by rank `src` during this launch; wait (bounded)
+// for its flag first.
 template <int W, bool ADAM, int MODE>
-__device__ __forceinline__ void load_item(Walk<W>& w, int t0, int t1, int wait_src, int wait_row) {
-    constexpr int G = MODE == REDUCE_PUSH ? W : 1;
+__device__ __forceinline__ void load_item(Walk<W>& w, int t0, int t1, int wait_row) {
+    constexpr int GS = kGatherSubs<W, ADAM>, SL = kGatherSlots<ADAM>;
     const Pipe& pp = w.pp;
     if (*w.abort()) return;
-    if (wait_src >= 0) {
-        const unsigned* f = w.c.flags[w.me] + flag_index(wait_row, w.block, wait_src);
+    if (wait_row >= 0) {
+        const unsigned* f = w.c.flags[w.me] + flag_index(wait_row, w.block, w.src);
         const unsigned long long start = global_ns();
         while ((int)(ld_acquire_sys(f) - w.a.seq) < 0) {
             if (global_ns() - start > w.a.timeout_ns) {
@@ -562,54 +633,79 @@ __device__ __forceinline__ void load_item(Walk<W>& w, int t0, int t1, int wait_s
         if (*w.abort()) return;
         int64_t base;
         bool adam;
-        if (!w.template ring_tile<ADAM, MODE>(t, &base, &adam)) continue;
-        for (int sub = 0; sub < kSubsPerTile; sub++, w.it++) {
+        if (!w.template ring_tile<ADAM>(t, &base, &adam)) continue;
+        const int per = MODE == REDUCE_OWN ? 1 : GS;
+        for (int sub = 0; sub < kSubsPerTile; sub += per, w.it++) {
             const int stage = w.it % pp.stages;
             if (!mbar_wait(pp.empty + stage, ((w.it / pp.stages) & 1) ^ 1, w.a, w.c, w.abort())) return;
             unsigned char* dst = pp.data + (size_t)stage * pp.stage_bytes;
-            const int64_t off = base + sub * kSub;
-            mbar_arrive_expect(pp.full + stage, (unsigned)((G + (adam ? 3 : 0)) * kSubBytes));
-            if (MODE == REDUCE_PUSH) {
+            uint64_t* bar = pp.full + stage;
+            if (MODE == REDUCE_OWN) {
+                const int64_t off = base + sub * kSub;
+                mbar_arrive_expect(bar, (unsigned)((W + (adam ? 3 : 0)) * kSubBytes));
 #pragma unroll
-                for (int r = 0; r < W; r++) bulk_load(dst + r * kSubBytes, w.s.g[r] + off, kSubBytes, pp.full + stage);
+                for (int r = 0; r < W; r++) bulk_load(dst + r * kSubBytes, w.s.g[r] + off, kSubBytes, bar);
+                if (adam) {
+                    bulk_load(dst + W * kSubBytes, w.s.p + off, kSubBytes, bar);
+                    bulk_load(dst + (W + 1) * kSubBytes, w.s.m + off, kSubBytes, bar);
+                    bulk_load(dst + (W + 2) * kSubBytes, w.s.v + off, kSubBytes, bar);
+                }
             } else {
-                bulk_load(dst, w.s.gme + off, kSubBytes, pp.full + stage);
-            }
-            if (adam) {
-                bulk_load(dst + G * kSubBytes, w.s.p + off, kSubBytes, pp.full + stage);
-                bulk_load(dst + (G + 1) * kSubBytes, w.s.m + off, kSubBytes, pp.full + stage);
-                bulk_load(dst + (G + 2) * kSubBytes, w.s.v + off, kSubBytes, pp.full + stage);
+                mbar_arrive_expect(bar, (unsigned)(per * (1 + (adam ? 3 : 0)) * kSubBytes));
+#pragma unroll
+                for (int q = 0; q < per; q++) {
+                    const int64_t off = base + (sub + q) * kSub;
+                    unsigned char* d = dst + q * SL * kSubBytes;
+                    bulk_load(d, w.s.gsrc + off, kSubBytes, bar);  // crosses NVLink unless src == me
+                    if (adam) {
+                        bulk_load(d + kSubBytes, w.s.p + off, kSubBytes, bar);
+                        bulk_load(d + 2 * kSubBytes, w.s.m + off, kSubBytes, bar);
+                        bulk_load(d + 3 * kSubBytes, w.s.v + off, kSubBytes, bar);
+                    }
+                }
             }
         }
     }
 }
 
-// ---- compute warps: 256 threads, one float4 of every stream each, in place in shared memory.
+// ---- compute warps: 256 threads, one float4 of every stream and sub-tile each, in place in shared memory.
 template <int W, bool ADAM, int MODE>
 __device__ __forceinline__ void compute_item(Walk<W>& w, int t0, int t1) {
-    constexpr int G = MODE == REDUCE_PUSH ? W : 1;
+    constexpr int GS = kGatherSubs<W, ADAM>, SL = kGatherSlots<ADAM>;
     const Pipe& pp = w.pp;
     for (int t = t0; t < t1; t++) {
         if (*w.abort()) return;
         int64_t base;
         bool adam;
-        if (!w.template ring_tile<ADAM, MODE>(t, &base, &adam)) continue;
+        if (!w.template ring_tile<ADAM>(t, &base, &adam)) continue;
         const Hyper& h = w.a.hp[w.s.hyper];
-        for (int sub = 0; sub < kSubsPerTile; sub++, w.it++) {
+        const int per = MODE == REDUCE_OWN ? 1 : GS;
+        for (int sub = 0; sub < kSubsPerTile; sub += per, w.it++) {
             const int stage = w.it % pp.stages;
             if (!mbar_wait(pp.full + stage, (w.it / pp.stages) & 1, w.a, w.c, w.abort())) return;
             float4* st = reinterpret_cast<float4*>(pp.data + (size_t)stage * pp.stage_bytes) + threadIdx.x;
-            float4 avg = st[0];
-            if (MODE == REDUCE_PUSH) {
+            if (MODE == REDUCE_OWN) {
+                float4 avg = st[0];
 #pragma unroll
                 for (int r = 1; r < W; r++) avg = add4(avg, st[r * kThreads]);
-                avg = mul4(avg, w.a.inv_world);
-                st[0] = avg;
-            }
-            if (adam) {
-                float4 p = st[G * kThreads], m = st[(G + 1) * kThreads], v = st[(G + 2) * kThreads];
-                adamw_vec(p, avg, m, v, h, w.s.wd);
-                st[G * kThreads] = p, st[(G + 1) * kThreads] = m, st[(G + 2) * kThreads] = v;
+                if (W > 1) {
+                    avg = mul4(avg, w.a.inv_world);
+                    st[0] = avg;
+                }
+                if (adam) {
+                    float4 p = st[W * kThreads], m = st[(W + 1) * kThreads], v = st[(W + 2) * kThreads];
+                    adamw_vec(p, avg, m, v, h, w.s.wd);
+                    st[W * kThreads] = p, st[(W + 1) * kThreads] = m, st[(W + 2) * kThreads] = v;
+                }
+            } else if (adam) {
+#pragma unroll
+                for (int q = 0; q < per; q++) {
+                    float4* sq = st + q * SL * kThreads;
+                    const float4 avg = sq[0];
+                    float4 p = sq[kThreads], m = sq[2 * kThreads], v = sq[3 * kThreads];
+                    adamw_vec(p, avg, m, v, h, w.s.wd);
+                    sq[kThreads] = p, sq[2 * kThreads] = m, sq[3 * kThreads] = v;
+                }
             }
             fence_async_proxy_smem();  // the bulk stores read what was just written through the generic proxy
             mbar_arrive(pp.computed + stage);
@@ -620,38 +716,46 @@ __device__ __forceinline__ void compute_item(Walk<W>& w, int t0, int t1) {
 // ---- storer: one thread. post_row >= 0: once every store of the item has landed, publish the flag to all peers.
 template <int W, bool ADAM, int MODE>
 __device__ __forceinline__ void store_item(Walk<W>& w, int t0, int t1, int post_row) {
-    constexpr int G = MODE == REDUCE_PUSH ? W : 1;
+    constexpr int GS = kGatherSubs<W, ADAM>, SL = kGatherSlots<ADAM>;
     const Pipe& pp = w.pp;
     for (int t = t0; t < t1; t++) {
         if (*w.abort()) break;
         int64_t base;
         bool adam;
-        if (!w.template ring_tile<ADAM, MODE>(t, &base, &adam)) continue;
-        for (int sub = 0; sub < kSubsPerTile; sub++, w.it++) {
+        if (!w.template ring_tile<ADAM>(t, &base, &adam)) continue;
+        const int per = MODE == REDUCE_OWN ? 1 : GS;
+        for (int sub = 0; sub < kSubsPerTile; sub += per, w.it++) {
             const int stage = w.it % pp.stages;
             if (!mbar_wait(pp.computed + stage, (w.it / pp.stages) & 1, w.a, w.c, w.abort())) break;
             const unsigned char* src = pp.data + (size_t)stage * pp.stage_bytes;
-            const int64_t off = base + sub * kSub;
-            if (MODE == REDUCE_PUSH) {
+            if (MODE == REDUCE_OWN) {
+                const int64_t off = base + sub * kSub;
+                if (W > 1) bulk_store(w.s.gme + off, src, kSubBytes);  // the mean: peers pull it from here
+                if (adam) {
+                    bulk_store(w.s.p + off, src + W * kSubBytes, kSubBytes);
+                    bulk_store(w.s.m + off, src + (W + 1) * kSubBytes, kSubBytes);
+                    bulk_store(w.s.v + off, src + (W + 2) * kSubBytes, kSubBytes);
+                }
+            } else {
 #pragma unroll
-                for (int r = 0; r < W; r++) bulk_store(w.s.g[r] + off, src, kSubBytes);  // r != me crosses NVLink
-            }
-            if (adam) {
-                bulk_store(w.s.p + off, src + G * kSubBytes, kSubBytes);
-                bulk_store(w.s.m + off, src + (G + 1) * kSubBytes, kSubBytes);
-                bulk_store(w.s.v + off, src + (G + 2) * kSubBytes, kSubBytes);
+                for (int q = 0; q < per; q++) {
+                    const int64_t off = base + (sub + q) * kSub;
+                    const unsigned char* sq = src + q * SL * kSubBytes;
+                    if (w.src != w.me) bulk_store(w.s.gme + off, sq, kSubBytes);  // the local gradient holds the mean too
+                    if (adam) {
+                        bulk_store(w.s.p + off, sq + kSubBytes, kSubBytes);
+                        bulk_store(w.s.m + off, sq + 2 * kSubBytes, kSubBytes);
+                        bulk_store(w.s.v + off, sq + 3 * kSubBytes, kSubBytes);
+                    }
+                }
             }
             bulk_commit();
-            bulk_wait_read<1>();  // all but the newest group have read their stage: the previous one is free again
-            if (w.prev >= 0) mbar_arrive(pp.empty + w.prev);
-            w.prev = stage;
+            bulk_wait_read<0>();  // the stores have read the stage: it can be refilled
+            mbar_arrive(pp.empty + stage);
         }
     }
     if (post_row >= 0) {
-        bulk_wait_read<0>();
-        if (w.prev >= 0) mbar_arrive(pp.empty + w.prev);
-        w.prev = -1;
-        bulk_wait_all();  // every byte of the item, local or on a peer, has landed
+        bulk_wait_all();  // every byte of the item has landed
         fence_async_proxy();
         __threadfence_system();
 #pragma unroll
@@ -660,24 +764,16 @@ __device__ __forceinline__ void store_item(Walk<W>& w, int t0, int t1, int post_
     }
 }
 
-// storer, end of kernel: hand back the last stage and wait for the last stores
-template <int W>
-__device__ __forceinline__ void store_drain(Walk<W>& w) {
-    bulk_wait_read<0>();
-    if (w.prev >= 0) mbar_arrive(w.pp.empty + w.prev);
-    w.prev = -1;
-    bulk_wait_all();
-    fence_async_proxy();
-}
-
-// One item, whichever role the calling thread has.
+// One item, whichever role the calling thread has. src: the rank whose gradient memory a GATHER item reads.
 template <int W, bool ADAM, int MODE>
-__device__ __forceinline__ void run_item(Walk<W>& w, int role, int t0, int t1, int wait_src, int wait_row, int post_row) {
+__device__ __forceinline__ void run_item(Walk<W>& w, int role, int t0, int t1, int src, int wait_row, int post_row) {
+    if (role > 2) return;
+    w.set_src(src);
     if (role == 0)
         compute_item<W, ADAM, MODE>(w, t0, t1);
     else if (role == 1)
-        load_item<W, ADAM, MODE>(w, t0, t1, wait_src, wait_row);
-    else if (role == 2)
+        load_item<W, ADAM, MODE>(w, t0, t1, wait_row);
+    else
         store_item<W, ADAM, MODE>(w, t0, t1, post_row);
 }
 
@@ -716,13 +812,13 @@ __global__ void __launch_bounds__(kPipeThreads, 2) k_step(const __grid_constant_
 
     if (W == 1) {
         const int t0 = cut(T, b, G), t1 = cut(T, b + 1, G);
-        ragged_pass<W, ADAM, LOCAL>(w, t0, t1);
-        run_item<W, ADAM, LOCAL>(w, role, t0, t1, -1, 0, -1);
-        if (role == 2) store_drain<W>(w);
+        ragged_pass<W, ADAM, REDUCE_OWN>(w, t0, t1, me);
+        run_item<W, ADAM, GATHER>(w, role, t0, t1, me, -1, -1);
+        if (role == 2) bulk_wait_all();
         return;
     }
 
-    // The run of block b inside chunk ch, and slice j of that run.
+    // The run of block b inside chunk ch.
     auto run_of = [&](int ch, int* r0, int* r1) {
         const int cb = cut(T, ch, W), L = cut(T, ch + 1, W) - cb;
         *r0 = cb + cut(L, b, G), *r1 = cb + cut(L, b + 1, G);
@@ -733,17 +829,17 @@ __global__ void __launch_bounds__(kPipeThreads, 2) k_step(const __grid_constant_
     post<W>(c, B_START, b, me, a.seq);
     await<W>(c, a, B_START, b, me, -1, ST_TIMEOUT_START, pp.abort);
     // ragged tiles of the own chunk first, published through the block-wide barrier row
-    if (!*pp.abort) ragged_pass<W, ADAM, REDUCE_PUSH>(w, own0, own1);
+    if (!*pp.abort) ragged_pass<W, ADAM, REDUCE_OWN>(w, own0, own1, me);
     post<W>(c, B_REDUCED, b, me, a.seq);
 
     // Whole tiles: the own chunk slice by slice, each slice's mean published as soon as its stores have landed;
-    // one slice behind, the same slice of every other chunk is picked up from local memory. Pulls over NVLink and
-    // the purely local updates therefore overlap instead of following one another.
+    // one slice behind, the same slice of every other chunk is pulled from its owner. No block ever waits for a
+    // whole phase of a peer, only for the slice it is about to read, which the peer finished a slice ago.
     for (int j = 0; j <= kSlices; j++) {
         if (j < kSlices) {
             const int len = own1 - own0;
-            run_item<W, ADAM, REDUCE_PUSH>(w, role, own0 + cut(len, j, kSlices), own0 + cut(len, j + 1, kSlices), -1, 0,
-                                           B_SLICE + j);
+            run_item<W, ADAM, REDUCE_OWN>(w, role, own0 + cut(len, j, kSlices), own0 + cut(len, j + 1, kSlices), me, -1,
+                                          B_SLICE + j);
         }
         if (j >= 1) {
             for (int k = 1; k < W; k++) {
@@ -751,23 +847,28 @@ __global__ void __launch_bounds__(kPipeThreads, 2) k_step(const __grid_constant_
                 int r0, r1;
                 run_of(src, &r0, &r1);
                 const int len = r1 - r0;
-                // without an optimizer the item moves nothing; the loader still waits, so that the kernel only ends
-                // once every owner has written its slices into this rank's gradient
-                run_item<W, ADAM, LOCAL>(w, role, r0 + cut(len, j - 1, kSlices), r0 + cut(len, j, kSlices), src,
-                                         B_SLICE + j - 1, -1);
+                run_item<W, ADAM, GATHER>(w, role, r0 + cut(len, j - 1, kSlices), r0 + cut(len, j, kSlices), src,
+                                          B_SLICE + j - 1, -1);
             }
         }
     }
-    if (role == 2) store_drain<W>(w);
+    if (role == 2) {
+        bulk_wait_all();
+        fence_async_proxy();
+    }
     __syncwarp();
-    await<W>(c, a, B_REDUCED, b, me, -1, ST_TIMEOUT_REDUCED, pp.abort);  // the peers' ragged tiles have arrived
-    if (ADAM && !*pp.abort) {
+    await<W>(c, a, B_REDUCED, b, me, -1, ST_TIMEOUT_REDUCED, pp.abort);  // the peers' ragged tiles are reduced
+    if (!*pp.abort) {
         for (int k = 1; k < W; k++) {
+            const int src = (me + k) % W;
             int r0, r1;
-            run_of((me + k) % W, &r0, &r1);
-            ragged_pass<W, ADAM, LOCAL>(w, r0, r1);
+            run_of(src, &r0, &r1);
+            ragged_pass<W, ADAM, GATHER>(w, r0, r1, src);
         }
     }
+    // nobody may reuse or free gradient memory that a peer is still reading
+    post<W>(c, B_DONE, b, me, a.seq);
+    await<W>(c, a, B_DONE, b, me, -1, ST_TIMEOUT_DONE, pp.abort);
 }
 
 // ---------------------------------------------------------------- small elementwise kernels next to the path

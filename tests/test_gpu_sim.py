@@ -6,7 +6,7 @@ import pytest
 
 from oracle import pyoracle
 from soliton_b200 import workload
-from soliton_b200._C import counter
+from soliton_b200._C import counter, set_option
 from tests.gpu_util import DevBuf, sim_step, zeros
 
 pytestmark = pytest.mark.gpu
@@ -38,9 +38,17 @@ def oracle_steps(p0, g_by_step, sizes, wds, world):
     return ref, means
 
 
+@pytest.fixture(params=[0, 1], ids=["k_twoshot", "k_step"])
+def large_kernel(request):
+    """Runs a test once with each of the two kernels that take large steps."""
+    set_option("pipeline", request.param)
+    yield request.param
+    set_option("pipeline", -1)
+
+
 @pytest.mark.parametrize("mode", [1, 2], ids=["oneshot", "twoshot"])
 @pytest.mark.parametrize("world", [2, 3, 4, 8])
-def test_fused_step_matches_oracle_and_ranks_agree(cuda, world, mode):
+def test_fused_step_matches_oracle_and_ranks_agree(cuda, world, mode, large_kernel):
     p0, g0, p, g, m, v = make_case(world, SIZES)
     rc, status = sim_step(world, SIZES, p, g, m, v, WDS, H, 1, adam=True, mode=mode)
     assert rc == 0 and status == [0] * world
@@ -55,7 +63,7 @@ def test_fused_step_matches_oracle_and_ranks_agree(cuda, world, mode):
 
 
 @pytest.mark.parametrize("world", [2, 8])
-def test_bare_allreduce_mean_without_optimizer(cuda, world):
+def test_bare_allreduce_mean_without_optimizer(cuda, world, large_kernel):
     _, g0, p, g, m, v = make_case(world, SIZES)
     for mode in (1, 2):
         for r in range(world):
@@ -69,7 +77,7 @@ def test_bare_allreduce_mean_without_optimizer(cuda, world):
                 np.testing.assert_array_equal(g[r][s].get(), want)
 
 
-def test_three_steps_unaligned_pointers_and_block_counts(cuda):
+def test_three_steps_unaligned_pointers_and_block_counts(cuda, large_kernel):
     world, sizes, wds = 4, [2048 * 5 + 3, 999, 2048], [0.1, 0.0, 0.1]
     results = []
     for skew, blocks, mode in [(0, 0, 2), (1, 1, 2), (0, 3, 2), (3, 2, 1), (0, 0, 1)]:
@@ -95,7 +103,7 @@ def test_three_steps_unaligned_pointers_and_block_counts(cuda):
             np.testing.assert_array_equal(a, b)
 
 
-def test_large_single_buffer_two_shot_world_8(cuda):
+def test_large_single_buffer_two_shot_world_8(cuda, large_kernel):
     world, n = 8, 3_000_000
     p0, g0, p, g, m, v = make_case(world, [n])
     rc, status = sim_step(world, [n], p, g, m, v, [0.1], H, 1, mode=0)
@@ -107,7 +115,7 @@ def test_large_single_buffer_two_shot_world_8(cuda):
         np.testing.assert_array_equal(p[r][0].get(), ref[0][0])
 
 
-def test_missing_rank_makes_waits_run_out_and_the_device_stays_usable(cuda):
+def test_missing_rank_makes_waits_run_out_and_the_device_stays_usable(cuda, large_kernel):
     world = 2
     p0, g0, p, g, m, v = make_case(world, [5000])
     for mode, code in ((2, 21), (1, 22)):
