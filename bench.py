@@ -47,6 +47,7 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--mode", type=int, default=0, help="0 auto, 1 one-shot, 2 two-shot")
     ap.add_argument("--blocks-per-sm", type=int, default=0)
+    ap.add_argument("--bare", action="store_true", help="gradient mean only, no optimizer update (link-bound floor)")
     ap.add_argument("--pipeline", type=int, default=-1, help="-1 auto, 1 k_step (shared-memory ring), 0 k_twoshot")
     return ap.parse_args()
 
@@ -218,7 +219,10 @@ def run_ours(args, rank, local_rank, world):
 
     def step():
         distributed.all_reduce_grads(opt.params)
-        opt.step()
+        if args.bare:
+            lib.slb_flush()
+        else:
+            opt.step()
 
     def fence():
         lib.slb_flush()
@@ -301,6 +305,7 @@ def run_ours(args, rank, local_rank, world):
         "scaling": "weak", "vs_baseline": None, "dtype": "f32 (p update in f64)", "data": "synthetic",
         "config": {"workload": name, "params_per_rank": P, "world": world, "l2": "inputs larger than L2, no flush",
                    "exchange": {0: "none", 1: "one-shot", 2: "two-shot"}[mode], "blocks_per_rank": blocks,
+                   "optimizer": "none (--bare)" if args.bare else "AdamW",
                    "e2e_copies": "h2d: this step's gradients from pinned memory; d2h: updated parameters"},
         "roofline": roof,
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": 4 * P, "d2h_bytes_per_step": 4 * P,

@@ -37,15 +37,15 @@ extern "C" {
 void* sl_alloc(int dev, size_t n);
 /* core/soliton/api.d:138-141 (Pool.release, alloc.d:176-200). n is the unrounded size given to sl_alloc. */
 void sl_free(int dev, void* p, size_t n);
-/* core/soliton/api.d:143-154. out: allocated, reserved, peak_allocated, peak_reserved, n_alloc, n_raw, trace_hash */
+/* core/soliton/api.d:144-154. out: allocated, reserved, peak_allocated, peak_reserved, n_alloc, n_raw, trace_hash */
 void sl_stats(int dev, int64_t* out7);
 /* core/soliton/api.d:156-164 */
 void sl_reset_stats(int dev);
-/* core/soliton/api.d:166-169 */
+/* core/soliton/api.d:165-168 */
 void sl_empty_cache(int dev);
 /* core/soliton/api.d:256-260. 0 = unlimited. */
 void sl_set_limit(int dev, int64_t bytes);
-/* core/soliton/api.d:173-215: trace recording for the arena planner */
+/* core/soliton/api.d:172-215: trace recording for the arena planner */
 void sl_record_start(int dev);
 void sl_record_stop(int dev);
 void sl_record_mark(int dev);
@@ -55,7 +55,7 @@ void sl_record_get(int dev, int64_t* size, int64_t* start, int64_t* end);
 /* core/soliton/api.d:217-238. The two arrays stay owned by the caller and must outlive the install. 0 or -2. */
 int sl_arena_install(int dev, const int64_t* offsets, const int64_t* sizes, int64_t count, int64_t body,
                      int64_t arena_bytes);
-/* core/soliton/api.d:240-244 */
+/* core/soliton/api.d:241-244 */
 int sl_arena_diverged(int dev);
 /* core/soliton/api.d:246-254 */
 void sl_arena_off(int dev);
@@ -67,11 +67,11 @@ void sl_arena_off(int dev);
  * staging) -- the only scratch the path ever uses, taken once and in this fixed order on both devices, so a meta
  * dry run predicts the cuda pool exactly. 0, -1 (no such device) or -2 (out of memory). */
 int sl_init_device(int dev, int ordinal);
-/* core/soliton/api.d:275-278 */
+/* core/soliton/api.d:276-279 */
 int sl_cuda_count(void);
-/* core/soliton/api.d:280-283. Sticky error code, 0 when none. */
+/* core/soliton/api.d:281-284. Sticky error code, 0 when none. */
 int sl_check(int dev);
-/* core/soliton/api.d:285-289. Launches whatever step is pending, then waits for the device. */
+/* core/soliton/api.d:286-290. Launches whatever step is pending, then waits for the device. */
 void sl_sync(int dev);
 /* core/soliton/api.d:299-302 */
 void sl_mem_info(size_t* free_bytes, size_t* total_bytes);
@@ -105,10 +105,10 @@ void sl_dist_destroy(void);
 
 /* ------------------------------------------------------------------ sl_*: next to the path (gradient clipping, accumulation) */
 
-/* core/soliton/api.d:363-376 (python/soliton/optim.py:31-39 uses sumsq + scale; tensor.py:451-462 uses axpy) */
+/* core/soliton/api.d:364-372 (python/soliton/optim.py:31-39 uses sumsq + scale; tensor.py:451-462 uses axpy) */
 void sl_axpy(int dev, const float* x, float* y, int64_t n, float alpha);
 void sl_scale(int dev, const float* x, float* y, int64_t n, float alpha);
-/* core/soliton/api.d:378-382. Blocking. NaN on meta. */
+/* core/soliton/api.d:379-382. Blocking. NaN on meta. */
 double sl_sumsq(int dev, const float* x, int64_t n);
 
 /* ------------------------------------------------------------------ 2. sl_cuda_*: backend level */

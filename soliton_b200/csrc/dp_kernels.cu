@@ -295,63 +295,6 @@ __device__ __forceinline__ void do_tile(const SegView<W>& s, const LaunchArgs& a
     }
 }
 
-// Several whole tiles of one segment at once (k_twoshot only): every peer load of the group is issued before the
-// first tile is touched, so that a thread has kGroup x 2 x (streams) 16-byte NVLink loads outstanding instead of
-// 2 x (streams). The all-gather half of the exchange has a single remote stream and needs that depth to cover
-// the NVLink round trip; the reduce half needs it at small world sizes.
-template <int W, int MODE>
-constexpr int kGroup = MODE == GATHER ? 4 : (W >= 5 ? 1 : (W >= 3 ? 2 : 4));
-
-template <int W, bool ADAM, int MODE>
-__device__ __forceinline__ void do_group(const SegView<W>& s, const LaunchArgs& a, int t, int me) {
-    constexpr int U = kTile / (4 * kThreads), GR = kGroup<W, MODE>, NS = MODE == GATHER ? 1 : W;
-    const int tid = threadIdx.x;
-    const int64_t base = (int64_t)(t - s.first_tile) * kTile;
-    const Hyper& h = a.hp[s.hyper];
-    const bool adam = ADAM && s.p != nullptr;
-    float4 gv[GR][U][NS];
-#pragma unroll
-    for (int k = 0; k < GR; k++)
-#pragma unroll
-        for (int u = 0; u < U; u++) {
-            const int64_t off = base + (int64_t)k * kTile + (tid + u * kThreads) * 4;
-            if (MODE == GATHER) {
-                gv[k][u][0] = ld_sys4(s.gsrc + off);
-            } else {
-#pragma unroll
-                for (int r = 0; r < W; r++) gv[k][u][r] = ld_sys4(s.g[r] + off);
-            }
-        }
-#pragma unroll
-    for (int k = 0; k < GR; k++) {
-        float4 pv[U], mv[U], vv[U];
-        if (adam) {
-#pragma unroll
-            for (int u = 0; u < U; u++) {
-                const int64_t off = base + (int64_t)k * kTile + (tid + u * kThreads) * 4;
-                pv[u] = ld_stream4(s.p + off), mv[u] = ld_stream4(s.m + off), vv[u] = ld_stream4(s.v + off);
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < U; u++) {
-            const int64_t off = base + (int64_t)k * kTile + (tid + u * kThreads) * 4;
-            float4 avg = gv[k][u][0];
-            if (MODE != GATHER) {
-#pragma unroll
-                for (int r = 1; r < W; r++) avg = add4(avg, gv[k][u][r]);
-                avg = mul4(avg, a.inv_world);
-            }
-            st_stream4(s.gme + off, avg);
-            if (adam) {
-                adamw_vec(pv[u], avg, mv[u], vv[u], h, s.wd);
-                st_stream4(s.p + off, pv[u]);
-                st_stream4(s.m + off, mv[u]);
-                st_stream4(s.v + off, vv[u]);
-            }
-        }
-    }
-}
-
 template <int W, bool ADAM, int MODE>
 __device__ __forceinline__ void do_run(const LaunchArgs& a, const RankCtx& c, const int* prefix, int t0, int t1, int me,
                                        int src, const float* stage, size_t stage_off) {
@@ -359,15 +302,6 @@ __device__ __forceinline__ void do_run(const LaunchArgs& a, const RankCtx& c, co
     s.first_tile = 0, s.end_tile = 0;
     for (int t = t0; t < t1; t++) {
         if (t >= s.end_tile || t < s.first_tile) load_seg<W>(s, c, prefix, t, me, src);
-        if (W > 1 && (MODE == GATHER || MODE == REDUCE_OWN)) {
-            constexpr int GR = kGroup<W, (MODE == GATHER ? GATHER : REDUCE_OWN)>;
-            // the next GR tiles lie in this run, in this segment, and are whole and aligned
-            if (GR > 1 && s.vec && t + GR <= t1 && (int64_t)(t + GR - s.first_tile) * kTile <= s.n) {
-                do_group<W, ADAM, (MODE == GATHER ? GATHER : REDUCE_OWN)>(s, a, t, me);
-                t += GR - 1;
-                continue;
-            }
-        }
         do_tile<W, ADAM, MODE>(s, a, c, t, me, stage, stage_off);
     }
 }
