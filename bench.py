@@ -32,13 +32,13 @@ BYTES_PER_PARAM = 28            # algorithmic HBM bytes per parameter per rank
 NVLINK_GBS = 770.0              # measured peer copy bandwidth per direction on this pool (nominal 900)
 FALLBACK_HBM_GBS = 6650.0       # used only when MEASURED_PEAKS.json is absent
 # DRAM bytes per parameter of the dominant kernel from an ncu capture (profiles/), per world size; None = not captured
-NCU_DRAM_BYTES_PER_PARAM = {}
+NCU_DRAM_BYTES_PER_PARAM = {1: 27.18}  # profiles/k_twoshot_w1_flat256MiB_ncu.md
 
 
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default="124M", choices=["124M", "medium", "tiny"])
@@ -74,7 +74,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
