@@ -145,6 +145,16 @@ void slb_clear_error(void);
  * `blocks` works on inside chunk `chunk` of `world` (chunk = -1: inside the whole sequence). */
 int64_t slb_tile_count(const int64_t* n, int nseg);
 void slb_run_range(int64_t tiles, int world, int chunk, int blocks, int block, int64_t* begin, int64_t* end);
+/* No counterpart in the reference. The fused multi-tensor AdamW step of sl_adamw for callers that must not see this
+ * library allocate device memory and have given it no workspace -- a host core that owns and plans the whole device
+ * heap, as Soliton's does. The segment table lives in a fixed 59,904-byte device array inside the library image, so
+ * at most 512 tensors per call; the call makes no cudaMalloc / cudaFree. Arrays are host arrays of nseg entries
+ * (device pointers, element counts, per-tensor weight decay; wd may be NULL for none). Work goes to the legacy
+ * default stream. The first call on a device looks up the array's address: make it outside stream capture. All calls
+ * share the array; calls whose kernels could overlap on the GPU race. 0 ok, -1 bad argument, -2 more than 512
+ * tensors, -3 a CUDA call failed. */
+int slb_adamw_step_static(int nseg, float* const* p, const float* const* g, float* const* m, float* const* v,
+                          const int64_t* n, const float* wd, float lr, float b1, float b2, float eps, int step);
 /* Test hook: `world` ranks emulated on one GPU by one cooperative launch (blocks of all ranks resident together).
  * Pointer arrays are indexed [rank * nseg + segment]; p/m/v may be NULL when adam = 0. mode: 0 auto, 1 one-shot,
  * 2 two-shot. active_mask: bit r set = rank r takes part (a missing rank makes the others' waits run out).

@@ -67,6 +67,7 @@ _SIGS = {
     "slb_clear_error": (None, []),
     "slb_tile_count": (L, [LP, I]),
     "slb_run_range": (None, [L, I, I, I, I, LP, LP]),
+    "slb_adamw_step_static": (I, [I, PP, PP, PP, PP, LP, C.POINTER(F), F, F, F, F, I]),
     "slb_sim_step": (I, [I, I, LP, PP, PP, PP, PP, C.POINTER(F), F, F, F, F, I, I, I, I, L, C.c_uint, C.POINTER(I)]),
     "slb_rdv_selftest": (I, [C.c_char_p, I, I, I]),
     "slb_rdv_create_id": (I, [C.c_char_p]),

@@ -27,6 +27,9 @@
 // its own flags (so peers do not wait on it in turn) and returns normally.
 #include <cuda_runtime.h>
 
+#include <cmath>
+#include <cstring>
+
 #include "dp_launch.h"
 #include "dp_types.h"
 
@@ -942,3 +945,117 @@ int launch_sumsq_partials(const float* x, int64_t n, double* partials, int block
 }
 
 }  // namespace slb
+
+// ---------------------------------------------------------------- a fused AdamW step that allocates nothing
+
+namespace slb {
+
+// Some callers cannot let this library take device memory on their behalf. The case this was written for is a host
+// runtime that owns the whole device heap and plans it ahead of time -- Soliton's core does: every device byte goes
+// through its pool so that a dry run predicts the peak exactly, and an allocation made behind its back would make
+// that prediction wrong. Such a caller may also not have handed the library a workspace (sl_init_device or
+// sl_cuda_dp_set_workspace), which every other entry point of the path needs for its segment table.
+//
+// slb_adamw_step_static is the multi-tensor AdamW step (the k_twoshot<1, true> kernel, same arithmetic, same bits)
+// with that table in a fixed array that is part of the library image instead: kStaticMaxSegs tensors per call at
+// most, 59,904 bytes of device memory per GPU that loads the library, held until the process exits. The entry
+// point calls no cudaMalloc / cudaFree and nothing that allocates on its behalf; the table image is built in a
+// static host buffer and copied over with one cudaMemcpyAsync on the legacy default stream, ahead of the launch.
+//
+// The first call on a device looks up the array's device address (cudaGetSymbolAddress, with that device
+// current) and remembers it; make that first call outside any stream capture. All calls share the one array, which
+// keeps the previous call's table: every call overwrites the part it uses, including the status word that must start
+// at zero, so stale contents are harmless -- but two calls whose kernels overlap on the GPU (launched from different
+// threads or processes' streams that are not ordered with the legacy stream) would race on it. Calls from one thread
+// are ordered by the stream and safe.
+constexpr int kStaticMaxSegs = 512;
+constexpr size_t kStaticStatusOff = 192;   // behind the RankCtx (176 bytes)
+constexpr size_t kStaticPrefixOff = 256;   // (kStaticMaxSegs + 1) ints
+constexpr size_t kStaticSegOff = 2560;
+constexpr size_t kStaticBytes = kStaticSegOff + size_t(kStaticMaxSegs) * sizeof(Seg);
+static_assert(sizeof(RankCtx) <= kStaticStatusOff, "static scratch layout");
+static_assert(kStaticPrefixOff + (kStaticMaxSegs + 1) * sizeof(int) <= kStaticSegOff, "static scratch layout");
+
+static __device__ __align__(256) unsigned char g_static_step_scratch[kStaticBytes];
+
+// Device address of the array on the current device, looked up once per device. In host code the array's name is
+// only a handle for this lookup, never a pointer a kernel could use.
+static unsigned char* static_scratch_address() {
+    constexpr int kMaxDevices = 64;
+    static unsigned char* cached[kMaxDevices] = {nullptr};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    if (!cached[dev]) {
+        void* ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_static_step_scratch) != cudaSuccess || !ptr) {
+            cudaGetLastError();
+            return nullptr;
+        }
+        cached[dev] = static_cast<unsigned char*>(ptr);
+    }
+    return cached[dev];
+}
+
+}  // namespace slb
+
+// 0 on success; -1 bad argument; -2 more tensors (or tiles) than the fixed table holds; -3 a CUDA call failed.
+extern "C" int slb_adamw_step_static(int nseg, float* const* p, const float* const* g, float* const* m, float* const* v,
+                                     const int64_t* n, const float* wd, float lr, float b1, float b2, float eps,
+                                     int step) {
+    using namespace slb;
+    if (nseg < 1 || !p || !g || !m || !v || !n || step < 1) return -1;
+    if (nseg > kStaticMaxSegs) return -2;
+    unsigned char* dev = static_scratch_address();
+    if (!dev) return -3;
+
+    static unsigned char image[kStaticBytes];  // host copy of the part of the array this call uses
+    RankCtx* ctx = reinterpret_cast<RankCtx*>(image);
+    int* prefix = reinterpret_cast<int*>(image + kStaticPrefixOff);
+    Seg* segs = reinterpret_cast<Seg*>(image + kStaticSegOff);
+    memset(image, 0, kStaticSegOff);  // context, status word (must start at zero), prefix
+    int64_t tiles = 0;
+    for (int s = 0; s < nseg; s++) {
+        if (n[s] < 0) return -1;
+        const uintptr_t bits = reinterpret_cast<uintptr_t>(p[s]) | reinterpret_cast<uintptr_t>(g[s]) |
+                               reinterpret_cast<uintptr_t>(m[s]) | reinterpret_cast<uintptr_t>(v[s]);
+        if (n[s] > 0 && (!p[s] || !g[s] || !m[s] || !v[s] || (bits & 3))) return -1;
+        Seg& d = segs[s];
+        memset(&d, 0, sizeof d);
+        d.p = p[s], d.m = m[s], d.v = v[s], d.g[0] = const_cast<float*>(g[s]);
+        d.n = n[s], d.wd = wd ? wd[s] : 0.0f, d.hyper = 0, d.vec = (bits & 15) == 0;
+        prefix[s] = (int)tiles;
+        tiles += (n[s] + kTile - 1) / kTile;
+        if (tiles > 0x7fffffff) return -2;
+    }
+    prefix[nseg] = (int)tiles;
+    if (tiles == 0) return 0;
+    ctx->segs = reinterpret_cast<const Seg*>(dev + kStaticSegOff);
+    ctx->tile_prefix = reinterpret_cast<const int*>(dev + kStaticPrefixOff);
+    ctx->nseg = nseg, ctx->rank = 0, ctx->world = 1;
+    ctx->flags[0] = nullptr, ctx->stage[0] = nullptr;
+    ctx->status = reinterpret_cast<int*>(dev + kStaticStatusOff);
+    const size_t used = kStaticSegOff + (size_t)nseg * sizeof(Seg);
+    if (cudaMemcpyAsync(dev, image, used, cudaMemcpyHostToDevice, 0) != cudaSuccess) {
+        cudaGetLastError();
+        return -3;
+    }
+
+    int device = 0, sms = 0;
+    if (cudaGetDevice(&device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
+        return -3;
+    const size_t smem = (size_t)(nseg + 1) * sizeof(int);
+    const int per_sm = step_occupancy(1, true, KERNEL_PLAIN, smem);
+    if (per_sm < 1 || sms < 1) return -3;
+    const int64_t cap = (int64_t)per_sm * sms;
+    LaunchArgs a{};
+    a.ctxs = reinterpret_cast<const RankCtx*>(dev);
+    a.blocks_per_rank = (int)(tiles < cap ? tiles : cap);
+    a.inv_world = 1.0f;
+    Hyper& h = a.hp[0];
+    h.bc1 = 1.0 - pow((double)b1, (double)step), h.bc2 = 1.0 - pow((double)b2, (double)step);
+    h.rbc1 = 1.0 / h.bc1, h.rbc2 = 1.0 / h.bc2;
+    h.lr = lr, h.b1 = b1, h.b2 = b2, h.eps = eps, h.c1 = 1 - b1, h.c2 = 1 - b2;
+    return launch_step(1, true, KERNEL_PLAIN, false, a.blocks_per_rank, smem, a, 0) == 0 ? 0 : -3;
+}
+
