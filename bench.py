@@ -40,13 +40,14 @@ def parse():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-gpu"])
     ap.add_argument("--model", default="124M", choices=["124M", "medium", "tiny"])
     ap.add_argument("--flat", type=int, default=0, help="one flat buffer of this many bytes instead of a model")
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--mode", type=int, default=0, help="0 auto, 1 one-shot, 2 two-shot")
     ap.add_argument("--blocks-per-sm", type=int, default=0)
+    ap.add_argument("--sweep", action="store_true", help="bucket-size sweep 4 KB .. 1 GB, one-shot vs two-shot (N >= 2)")
     ap.add_argument("--bare", action="store_true", help="gradient mean only, no optimizer update (link-bound floor)")
     ap.add_argument("--pipeline", type=int, default=-1, help="-1 auto, 1 k_step (shared-memory ring), 0 k_twoshot")
     return ap.parse_args()
@@ -320,6 +321,155 @@ def run_ours(args, rank, local_rank, world):
         dist.destroy_process_group()
 
 
+def run_sweep(args, rank, local_rank, world):
+    """Flat fp32 buffers of 4^k bytes, k = 6..15, through the fused path with the exchange forced to one-shot (where the
+    buffer fits a staging slot) and to two-shot; one JSON line with a row per (size, exchange)."""
+    import torch
+    import torch.distributed as dist
+    torch.cuda.set_device(local_rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    from soliton_b200 import distributed, tensor as T, workload
+    from soliton_b200._C import counter, lib, set_option
+    H = workload.HYPER
+    T.set_device(local_rank)
+    T._dev(T.CUDA)
+    idt = torch.zeros(128, dtype=torch.uint8, device="cuda")
+    if rank == 0:
+        idt.copy_(torch.frombuffer(bytearray(distributed.unique_id()), dtype=torch.uint8))
+    dist.broadcast(idt, 0)
+    distributed.init_with_id(rank, world, bytes(idt.cpu().numpy().tobytes()))
+    rows = []
+    for k in range(6, 16):
+        nbytes = 4 ** k
+        n = nbytes // 4
+        p0, g0 = workload.flat_case(n, rank=rank)
+        p, g, m, v = T.tensor(p0, "cuda"), T.tensor(g0, "cuda"), T.zeros((n,), "cuda"), T.zeros((n,), "cuda")
+        steps = 200 if nbytes <= (1 << 24) else 30
+        for mode in (1, 2):
+            if mode == 1 and nbytes > (16 << 20) // (2 * world):
+                continue
+            set_option("mode", mode)
+
+            def step(t=[0]):
+                t[0] += 1
+                lib.sl_dist_group(T.CUDA, 1)
+                lib.sl_dist_allreduce_mean(T.CUDA, g.ptr, n)
+                lib.sl_dist_group(T.CUDA, 0)
+                lib.sl_adamw(T.CUDA, p.ptr, g.ptr, m.ptr, v.ptr, n, H["lr"], H["b1"], H["b2"], H["eps"], H["wd"], t[0])
+
+            for _ in range(5):
+                step()
+            lib.slb_flush()
+            torch.cuda.synchronize()
+            dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                step()
+            lib.slb_flush()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = torch.tensor([e0.elapsed_time(e1) / steps], device="cuda")
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+            us = float(ms.item()) * 1e3
+            rows.append({"bytes": nbytes, "exchange": "one-shot" if mode == 1 else "two-shot", "us_per_step": round(us, 2),
+                         "hbm_GBps_per_rank": round(BYTES_PER_PARAM * n / us / 1e3, 1),
+                         "nvlink_GBps_per_dir": round(8.0 * n * (world - 1) / world / us / 1e3, 1),
+                         "kernel_mode": counter("last_mode"), "blocks": counter("last_blocks")})
+        set_option("mode", 0)
+        del p, g, m, v
+    err = lib.sl_check(T.CUDA)
+    if rank == 0:
+        print(json.dumps({"metric": "bucket_sweep_fused_allreduce_adamw", "n_gpus": world, "sticky_error": err,
+                          "rows": rows}), flush=True)
+    distributed.destroy()
+    dist.destroy_process_group()
+
+
+def run_reference_gpu(args, rank, local_rank, world):
+    """The reference's own GPU path on this box: grouped ncclAllReduce(avg) per tensor, then one k_adamw launch per
+    tensor (core/cuda/kernels.cu:242-254,772-775), from the unmodified backend built into oracle/_ref/."""
+    import ctypes as C
+    import torch
+    import torch.distributed as dist
+    from oracle import build as obuild
+    if not os.path.exists(obuild.REF_SO):
+        if rank == 0:
+            print(json.dumps({"impl": "reference-gpu", "unavailable": "oracle/_ref/ not built (no reference checkout at build time)"}))
+        return
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("gloo")
+    R = C.CDLL(obuild.REF_SO)
+    assert R.sl_cuda_set_device(local_rank) == 0
+    R.sl_cuda_malloc.restype = C.c_void_p
+    R.sl_cuda_malloc.argtypes = [C.c_size_t]
+    R.sl_cuda_h2d.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
+    R.sl_cuda_adamw.argtypes = [C.c_void_p] * 4 + [C.c_int64] + [C.c_float] * 5 + [C.c_int]
+    R.sl_cuda_nccl_allreduce_mean.argtypes = [C.c_void_p, C.c_int64]
+    R.sl_cuda_fill.argtypes = [C.c_void_p, C.c_int64, C.c_float]
+    if world > 1:
+        idt = torch.zeros(128, dtype=torch.uint8)
+        if rank == 0:
+            buf = C.create_string_buffer(128)
+            assert R.sl_cuda_nccl_unique_id(buf) == 0
+            idt = torch.frombuffer(bytearray(buf.raw), dtype=torch.uint8).clone()
+        dist.broadcast(idt, 0)
+        assert R.sl_cuda_nccl_init(rank, world, C.create_string_buffer(bytes(idt.numpy().tobytes()), 128)) == 0
+    shapes, make_p, make_g, wds, name, np = make_workload(args)
+    from soliton_b200 import workload
+    H = workload.HYPER
+    bufs = []
+    for a, gr in zip(make_p(), make_g(rank)):
+        n = int(a.size)
+        ptrs = [R.sl_cuda_malloc(4 * n) for _ in range(4)]
+        R.sl_cuda_h2d(ptrs[0], np.ascontiguousarray(a).ctypes.data, 4 * n)
+        R.sl_cuda_h2d(ptrs[1], np.ascontiguousarray(gr).ctypes.data, 4 * n)
+        R.sl_cuda_fill(ptrs[2], n, 0.0)
+        R.sl_cuda_fill(ptrs[3], n, 0.0)
+        bufs.append((ptrs, n))
+    P = sum(n for _, n in bufs)
+    t = [0]
+
+    def step():
+        t[0] += 1
+        if world > 1:
+            R.sl_cuda_nccl_group(1)
+            for ptrs, n in bufs:
+                R.sl_cuda_nccl_allreduce_mean(ptrs[1], n)
+            R.sl_cuda_nccl_group(0)
+        for (ptrs, n), wd in zip(bufs, wds):
+            R.sl_cuda_adamw(ptrs[0], ptrs[1], ptrs[2], ptrs[3], n, H["lr"], H["b1"], H["b2"], H["eps"], wd, t[0])
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    R.sl_cuda_sync()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    R.sl_cuda_sync()
+    ms = torch.tensor([e0.elapsed_time(e1) / args.steps])
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    assert R.sl_cuda_check() == 0
+    if rank == 0:
+        m = float(ms.item())
+        print(json.dumps({"impl": "reference-gpu", "metric": "fused_allreduce_adamw_algorithmic_GBps",
+                          "value": world * BYTES_PER_PARAM * P / (m * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": world,
+                          "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": m, "higher_is_better": True,
+                          "config": {"workload": name, "params_per_rank": P, "world": world,
+                                     "path": "reference core/cuda/kernels.cu: grouped ncclAllReduce(avg) + k_adamw per tensor"},
+                          "gpu_launches_per_step": len(bufs) + (1 if world > 1 else 0)}), flush=True)
+    if world > 1:
+        R.sl_cuda_nccl_destroy()
+        dist.destroy_process_group()
+
+
 def main():
     args = parse()
     rank = int(os.environ.get("RANK", 0))
@@ -332,6 +482,10 @@ def main():
         sys.exit(subprocess.call(cmd + sys.argv[1:]))
     if args.impl == "reference":
         run_reference(args, rank, world)
+    elif args.impl == "reference-gpu":
+        run_reference_gpu(args, rank, local_rank, world)
+    elif args.sweep:
+        run_sweep(args, rank, local_rank, world)
     else:
         run_ours(args, rank, local_rank, world)
 
