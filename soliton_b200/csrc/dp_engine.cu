@@ -151,6 +151,19 @@ void Engine::adamw(float* p, const float* g, float* m, float* v, int64_t n, floa
     if (n <= 0) return;
     if (!p || !g || !m || !v || !aligned4(p) || !aligned4(g) || !aligned4(m) || !aligned4(v)) return set_error(ERR_BAD_ARG);
     const HyperKey key{lr, b1, b2, eps, step};
+    float gscale = 1.0f;  // an in-place scale of this gradient that is still deferred rides along with the update
+    {
+        auto sc = pending_scale_.find(const_cast<float*>(g));
+        if (sc != pending_scale_.end()) {
+            if (sc->second.first == n && !reduce_pending_) {
+                gscale = sc->second.second;
+                pending_scale_.erase(sc);
+                sumsq_cache_.erase(std::make_pair(g, n));  // the launch rewrites this gradient
+            } else {
+                flush_scales();
+            }
+        }
+    }
     if (reduce_pending_) {
         auto it = by_grad_.find(g);
         if (it != by_grad_.end() && !items_[it->second].p && items_[it->second].n == n) {
@@ -158,24 +171,24 @@ void Engine::adamw(float* p, const float* g, float* m, float* v, int64_t n, floa
             if (hi >= 0) {
                 StepItem& s = items_[it->second];
                 s.p = p, s.m = m, s.v = v, s.wd = wd, s.hyper = hi;
-                if (++attached_ == (int)items_.size() || opt.eager) flush();
+                if (++attached_ == (int)items_.size() || opt.eager) flush_step();
                 return;
             }
         }
-        flush();  // this update is not part of the pending all-reduce: finish that first
+        flush_step();  // this update is not part of the pending all-reduce: finish that first
     }
     if (in_group_) return set_error(ERR_BAD_ARG);  // an optimizer step inside an open group has no defined order
-    if (params_in_batch_.count(p) || items_.size() >= (size_t)kMaxSegs) flush();
+    if (params_in_batch_.count(p) || items_.size() >= (size_t)kMaxSegs) flush_step();
     int hi = hyper_index(key);
     if (hi < 0) {
-        flush();
+        flush_step();
         hi = hyper_index(key);
     }
     StepItem s;
-    s.g = const_cast<float*>(g), s.p = p, s.m = m, s.v = v, s.n = n, s.wd = wd, s.hyper = hi;
+    s.g = const_cast<float*>(g), s.p = p, s.m = m, s.v = v, s.n = n, s.wd = wd, s.hyper = hi, s.gscale = gscale;
     items_.push_back(s);
     params_in_batch_.insert(p);
-    if (opt.eager) flush();
+    if (opt.eager) flush_step();
 }
 
 int Engine::group(int start) {
@@ -198,7 +211,9 @@ int Engine::group(int start) {
     }
     reduce_pending_ = true;
     attached_ = 0;
-    if (opt.eager) flush();
+    sumsq_plan_.clear();  // a clip of this step asks for the sum of squares of exactly these gradients
+    for (const StepItem& it : items_) sumsq_plan_.push_back(TensorRef{it.g, it.n});
+    if (opt.eager) flush_step();
     return 0;
 }
 
@@ -219,7 +234,7 @@ int Engine::allreduce_mean(float* g, int64_t n) {
     return 0;
 }
 
-void Engine::flush() {
+void Engine::flush_step() {
     if (in_group_) return;  // an open group has nothing that may be launched yet
     if (!items_.empty()) {
         const int rc = launch_items(items_, hypers_, reduce_pending_);
@@ -228,6 +243,27 @@ void Engine::flush() {
     items_.clear(), hypers_.clear(), by_grad_.clear(), params_in_batch_.clear();
     reduce_pending_ = false;
     attached_ = 0;
+}
+
+// Everything deferred goes out: the pending step, in-place scales that no AdamW call picked up. What was learned
+// about this clip's sumsq calls becomes the plan for the next one; cached sums die, memory may change from here on.
+void Engine::flush() {
+    flush_step();
+    flush_scales();
+    if (!sumsq_learn_.empty()) {
+        sumsq_history_.insert(sumsq_history_.begin(), std::vector<TensorRef>());
+        sumsq_history_.front().swap(sumsq_learn_);
+        if (sumsq_history_.size() > 3) sumsq_history_.pop_back();
+    }
+    sumsq_cache_.clear();
+}
+
+void Engine::flush_scales() {
+    for (auto& kv : pending_scale_) {
+        if (launch_scale(kv.first, kv.first, kv.second.first, kv.second.second, 0)) set_error(ERR_LAUNCH);
+        launches++;
+    }
+    pending_scale_.clear();
 }
 
 static void fill_hyper(Hyper& h, const HyperKey& k) {
@@ -250,7 +286,7 @@ static int64_t build_table(const std::vector<StepItem>& items, int world, int ra
     for (size_t s = 0; s < nseg; s++) {
         const StepItem& it = items[s];
         Seg& d = segs[s];
-        d.p = it.p, d.m = it.m, d.v = it.v, d.n = it.n, d.wd = it.wd, d.hyper = it.hyper;
+        d.p = it.p, d.m = it.m, d.v = it.v, d.n = it.n, d.wd = it.wd, d.hyper = it.hyper, d.gscale = it.gscale;
         bool vec = aligned16(it.g) && (!it.p || (aligned16(it.p) && aligned16(it.m) && aligned16(it.v)));
         for (int r = 0; r < world; r++) {
             d.g[r] = (world == 1 || r == rank) ? it.g : peer_g[r][s];
@@ -372,6 +408,7 @@ int Engine::launch_items(std::vector<StepItem>& items, const std::vector<HyperKe
 
 void Engine::on_raw_free(void* base) {
     Engine& e = get();
+    e.sumsq_plan_.clear(), e.sumsq_learn_.clear(), e.sumsq_history_.clear();  // remembered addresses may die with this block
     auto it = e.export_ids_.find(base);
     if (it == e.export_ids_.end()) return;
     e.rdv_.mark_freed((uint32_t)it->second);
@@ -531,10 +568,20 @@ int Engine::exchange() {
 
 void Engine::scale(const float* x, float* y, int64_t n, float alpha) {
     if (!cuda_ready()) return set_error(ERR_NO_WORKSPACE);
-    flush();
     if (n > 0 && (!x || !y)) return set_error(ERR_BAD_ARG);
+    if (n <= 0) return;
+    if (x == y && !opt.eager) {
+        // In place (gradient clipping): remembered, and applied by the AdamW launch that consumes this gradient, or
+        // by a plain scale launch at the next point where anything could look at the memory.
+        flush_step();
+        if (pending_scale_.count(y)) flush_scales();
+        sumsq_cache_.clear();
+        pending_scale_[y] = std::make_pair(n, alpha);
+        return;
+    }
+    flush();
     if (launch_scale(x, y, n, alpha, 0)) set_error(ERR_LAUNCH);
-    launches += n > 0;
+    launches++;
 }
 void Engine::axpy(const float* x, float* y, int64_t n, float alpha) {
     if (!cuda_ready()) return set_error(ERR_NO_WORKSPACE);
@@ -554,24 +601,106 @@ void Engine::fill(float* p, int64_t n, float v) {
 // Sum of squares of a tensor (the reference: cublasSdot, core/cuda/kernels.cu:219-224, blocking). Fixed block
 // slices and a fixed combination order make the value reproducible run to run; double partials make it at least
 // as accurate as the float dot it stands in for.
+// One launch for the sum of squares of every tensor in `plan`; results land in sumsq_cache_.
+bool Engine::sumsq_batch(const std::vector<TensorRef>& plan) {
+    std::vector<SumsqSlice> slices;
+    for (const TensorRef& t : plan)
+        for (int64_t off = 0; off < t.n; off += kSumsqSlice)
+            slices.push_back(SumsqSlice{t.x + off, t.n - off < kSumsqSlice ? t.n - off : (int64_t)kSumsqSlice});
+    if (slices.empty() || slices.size() > (size_t)kMaxSumsqSlices) return false;
+    SumsqSlice* d_slices = reinterpret_cast<SumsqSlice*>(ws_ + kSliceTableOff);
+    double* d_part = reinterpret_cast<double*>(ws_ + kSlicePartialOff);
+    if (slices.size() != dev_slices_.size() || memcmp(slices.data(), dev_slices_.data(), slices.size() * sizeof(SumsqSlice)) != 0) {
+        if (cudaMemcpyAsync(d_slices, slices.data(), slices.size() * sizeof(SumsqSlice), cudaMemcpyHostToDevice, 0) != cudaSuccess) return false;
+        dev_slices_ = slices;
+    }
+    if (launch_sumsq_slices((int)slices.size(), d_slices, d_part, sm_count_ * 8, 0)) {
+        set_error(ERR_LAUNCH);
+        return false;
+    }
+    launches++;
+    std::vector<double> h(slices.size());
+    if (cudaMemcpy(h.data(), d_part, h.size() * sizeof(double), cudaMemcpyDeviceToHost) != cudaSuccess) {
+        set_error(ERR_SYNC);
+        return false;
+    }
+    size_t i = 0;
+    for (const TensorRef& t : plan) {
+        double sum = 0;
+        for (int64_t off = 0; off < t.n; off += kSumsqSlice) sum += h[i++];  // slice order: reproducible
+        sumsq_cache_[std::make_pair(t.x, t.n)] = sum;
+    }
+    return true;
+}
+
+// Sum of squares of a tensor (the reference: cublasSdot, core/cuda/kernels.cu:219-224, blocking). Fixed slices and
+// a fixed combination order make the value reproducible run to run; double partials make it at least as accurate
+// as the float dot it stands in for. Soliton's clip asks tensor by tensor (python/soliton/optim.py:34); the first
+// question is answered by summing every tensor the clip is expected to ask about -- the gradients of the group
+// that was just reduced, else the tensors of the previous clip -- in one launch, the rest from that launch.
 double Engine::sumsq(const float* x, int64_t n) {
     if (!cuda_ready()) {
         set_error(ERR_NO_WORKSPACE);
         return NAN;
     }
-    flush();
+    flush_step();
+    if (!pending_scale_.empty()) {
+        flush_scales();
+        sumsq_cache_.clear();
+    }
     if (n <= 0) return 0.0;
-    double* d = reinterpret_cast<double*>(ws_ + kPartialOff);
-    if (launch_sumsq_partials(x, n, d, kSumsqBlocks, 0)) set_error(ERR_LAUNCH);
-    launches++;
-    double h[kSumsqBlocks];
-    if (cudaMemcpy(h, d, sizeof h, cudaMemcpyDeviceToHost) != cudaSuccess) {
-        set_error(ERR_SYNC);
+    if (!x) {
+        set_error(ERR_BAD_ARG);
         return NAN;
     }
-    double s = 0;
-    for (int i = 0; i < kSumsqBlocks; i++) s += h[i];
-    return s;
+    sumsq_learn_.push_back(TensorRef{x, n});
+    auto hit = sumsq_cache_.find(std::make_pair(x, n));
+    if (hit != sumsq_cache_.end()) return hit->second;
+    // Known from the group that was just reduced or from one of the last few clips? Then sum everything those lists
+    // name (their union: equal-sized blocks can swap places from step to step, which shows up as the same address
+    // with another length). A stale entry costs a little arithmetic; its sum is that of the memory as it is now.
+    bool known = false;
+    std::vector<TensorRef> plan;
+    auto add_list = [&](const std::vector<TensorRef>& list) {
+        for (const TensorRef& t : list) {
+            known = known || (t.x == x && t.n == n);
+            bool dup = false;
+            for (const TensorRef& q : plan) dup = dup || (q.x == t.x && q.n == t.n);
+            void* base;
+            size_t size;
+            // only tensors inside the pool's own blocks: readable until a raw block is freed, which clears the lists
+            if (!dup && pool(DEV_CUDA).find_raw(t.x, &base, &size) &&
+                reinterpret_cast<const char*>(t.x + t.n) <= static_cast<char*>(base) + size)
+                plan.push_back(t);
+        }
+    };
+    if (!opt.eager) {
+        add_list(sumsq_plan_);
+        for (const auto& list : sumsq_history_) add_list(list);
+    }
+    if (known) {
+        bool mine = false;
+        for (const TensorRef& t : plan) mine = mine || (t.x == x && t.n == n);
+        if (mine && sumsq_batch(plan)) {
+            auto got = sumsq_cache_.find(std::make_pair(x, n));
+            if (got != sumsq_cache_.end()) return got->second;
+        }
+    }
+    if (!sumsq_batch(std::vector<TensorRef>{TensorRef{x, n}})) {
+        // more slices than the table holds: the single-tensor kernel with its fixed 1024 partials
+        double* d = reinterpret_cast<double*>(ws_ + kPartialOff);
+        if (launch_sumsq_partials(x, n, d, kSumsqBlocks, 0)) set_error(ERR_LAUNCH);
+        launches++;
+        double h[kSumsqBlocks];
+        if (cudaMemcpy(h, d, sizeof h, cudaMemcpyDeviceToHost) != cudaSuccess) {
+            set_error(ERR_SYNC);
+            return NAN;
+        }
+        double s = 0;
+        for (int i = 0; i < kSumsqBlocks; i++) s += h[i];
+        return s;
+    }
+    return sumsq_cache_[std::make_pair(x, n)];
 }
 
 // ---------------------------------------------------------------- single-GPU emulation of several ranks

@@ -11,6 +11,7 @@
 // sl_adamw calls are batched the same way into one multi-tensor launch.
 #pragma once
 #include <cstdint>
+#include <map>
 #include <unordered_map>
 #include <unordered_set>
 #include <vector>
@@ -36,6 +37,7 @@ struct StepItem {               // one tensor of a pending step
     int64_t n = 0;
     float wd = 0;
     int hyper = 0;
+    float gscale = 1.0f;        // in-place gradient scale folded into the update (clipping)
 };
 
 struct HyperKey {
@@ -72,7 +74,8 @@ public:
     int dist_unique_id(char* out);                  // api.d:572-575
     int dist_init(int rank, int world, const char* id);  // api.d:577-580
     void dist_destroy();                            // api.d:592-595
-    void flush();                                   // launch whatever is pending
+    void flush();                                   // launch whatever is pending: the step, deferred scales
+    void flush_step();                              // only the pending step (all-reduce and/or AdamW batch)
 
     // --- next to the path
     void scale(const float* x, float* y, int64_t n, float alpha);
@@ -133,6 +136,21 @@ private:
     uint64_t peer_version_[kMaxWorld] = {0};
     std::vector<float*> peer_g_[kMaxWorld];                             // per segment, rank r's gradient as mapped here
     std::vector<RdvSegment> my_table_;
+
+    // Gradient clipping next to the path (python/soliton/optim.py:31-39): the per-tensor sumsq calls of one clip are
+    // answered from one batched launch, and the in-place scales that follow are folded into the AdamW launch.
+    struct TensorRef {
+        const float* x;
+        int64_t n;
+    };
+    void flush_scales();
+    bool sumsq_batch(const std::vector<TensorRef>& plan);
+    std::vector<TensorRef> sumsq_plan_, sumsq_learn_;   // gradients of the last reduced group / tensors seen in this clip
+    std::vector<std::vector<TensorRef>> sumsq_history_; // tensor lists of the last few clips, newest first (the pool
+                                                        // hands equal-sized blocks out in an order that can alternate)
+    std::map<std::pair<const float*, int64_t>, double> sumsq_cache_;   // (address, elements) -> sum, until memory may change
+    std::unordered_map<float*, std::pair<int64_t, float>> pending_scale_;
+    std::vector<SumsqSlice> dev_slices_;
 
     // emulation
     char* sim_ws_ = nullptr;

@@ -156,7 +156,7 @@ struct SegView {
     float* gme;    // this rank's gradient
     float* gsrc;   // GATHER: the owner's gradient
     int64_t n;
-    float wd;
+    float wd, gscale;
     int hyper, vec;
     int first_tile, end_tile;  // [first, end) of this segment in the tile sequence
 };
@@ -183,7 +183,7 @@ __device__ __forceinline__ void load_seg(SegView<W>& s, const RankCtx& c, const 
     for (int r = 0; r < W; r++) s.g[r] = sg->g[r];
     s.gme = sg->g[me];
     s.gsrc = sg->g[src];
-    s.n = sg->n, s.wd = sg->wd, s.hyper = sg->hyper, s.vec = sg->vec;
+    s.n = sg->n, s.wd = sg->wd, s.gscale = sg->gscale, s.hyper = sg->hyper, s.vec = sg->vec;
     s.first_tile = prefix[i], s.end_tile = prefix[i + 1];
 }
 
@@ -250,6 +250,10 @@ __device__ __forceinline__ void do_tile(const SegView<W>& s, const LaunchArgs& a
                 for (int r = 1; r < W; r++) avg = add4(avg, gv[u][r]);
                 avg = mul4(avg, a.inv_world);
             }
+            if (W == 1 && s.gscale != 1.0f) {  // clipped gradient: y = alpha * x in float, kept in place
+                avg = mul4(avg, s.gscale);
+                st_stream4(s.gme + off, avg);
+            }
             if (W > 1) st_stream4(s.gme + off, avg);
             if (adam) {
                 adamw_vec(pv[u], avg, mv[u], vv[u], h, s.wd);
@@ -287,6 +291,10 @@ __device__ __forceinline__ void do_tile(const SegView<W>& s, const LaunchArgs& a
 #pragma unroll
                 for (int r = 1; r < W; r++) avg = __fadd_rn(avg, x[r]);
                 avg = __fmul_rn(avg, a.inv_world);
+            }
+            if (W == 1 && s.gscale != 1.0f) {
+                avg = __fmul_rn(s.gscale, avg);
+                s.gme[off] = avg;
             }
             if (W > 1) s.gme[off] = avg;
             if (adam) {
@@ -638,7 +646,11 @@ __device__ __forceinline__ void compute_item(Walk<W>& w, int t0, int t1) {
 #pragma unroll
                 for (int q = 0; q < per; q++) {
                     float4* sq = st + q * SL * kThreads;
-                    const float4 avg = sq[0];
+                    float4 avg = sq[0];
+                    if (W == 1 && w.s.gscale != 1.0f) {
+                        avg = mul4(avg, w.s.gscale);
+                        sq[0] = avg;
+                    }
                     float4 p = sq[kThreads], m = sq[2 * kThreads], v = sq[3 * kThreads];
                     adamw_vec(p, avg, m, v, h, w.s.wd);
                     sq[kThreads] = p, sq[2 * kThreads] = m, sq[3 * kThreads] = v;
@@ -678,7 +690,8 @@ __device__ __forceinline__ void store_item(Walk<W>& w, int t0, int t1, int post_
                 for (int q = 0; q < per; q++) {
                     const int64_t off = base + (sub + q) * kSub;
                     const unsigned char* sq = src + q * SL * kSubBytes;
-                    if (w.src != w.me) bulk_store(w.s.gme + off, sq, kSubBytes);  // the local gradient holds the mean too
+                    if (w.src != w.me || (W == 1 && w.s.gscale != 1.0f))
+                        bulk_store(w.s.gme + off, sq, kSubBytes);  // the local gradient holds the mean (or the clipped value) too
                     if (adam) {
                         bulk_store(w.s.p + off, sq + kSubBytes, kSubBytes);
                         bulk_store(w.s.m + off, sq + 2 * kSubBytes, kSubBytes);
@@ -845,6 +858,31 @@ __global__ void __launch_bounds__(kThreads) k_sumsq(int64_t n, const float* x, d
     }
 }
 
+// Sum of squares of many tensors in one launch: slice i (at most kSumsqSlice floats of one tensor) is summed by one
+// block in the same fixed order as k_sumsq, blocks take slices round robin; the host adds a tensor's partials in
+// slice order. Nothing depends on scheduling.
+__global__ void __launch_bounds__(kThreads) k_sumsq_slices(int nslices, const SumsqSlice* slices, double* partials) {
+    __shared__ double s_warp[kThreads / 32];
+    for (int i = blockIdx.x; i < nslices; i += gridDim.x) {
+        const float* x = slices[i].x;
+        const int64_t n = slices[i].n;
+        double acc = 0;
+        for (int64_t e = threadIdx.x; e < n; e += kThreads) {
+            const double v = (double)x[e];
+            acc = __fma_rn(v, v, acc);
+        }
+        for (int o = 16; o; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
+        __syncthreads();  // the previous slice's s_warp has been read
+        if ((threadIdx.x & 31) == 0) s_warp[threadIdx.x >> 5] = acc;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            double t = 0;
+            for (int w = 0; w < kThreads / 32; w++) t += s_warp[w];
+            partials[i] = t;
+        }
+    }
+}
+
 // ---------------------------------------------------------------- launch
 
 template <int W, bool ADAM>
@@ -939,6 +977,11 @@ int launch_fill(float* p, int64_t n, float value, cudaStream_t st) {
     return (int)cudaPeekAtLastError();
 }
 
+int launch_sumsq_slices(int nslices, const SumsqSlice* slices, double* partials, int blocks, cudaStream_t st) {
+    if (nslices <= 0) return 0;
+    k_sumsq_slices<<<blocks < nslices ? blocks : nslices, kThreads, 0, st>>>(nslices, slices, partials);
+    return (int)cudaPeekAtLastError();
+}
 int launch_sumsq_partials(const float* x, int64_t n, double* partials, int blocks, cudaStream_t st) {
     k_sumsq<<<blocks, kThreads, 0, st>>>(n, x, partials);
     return (int)cudaPeekAtLastError();
@@ -1022,7 +1065,7 @@ extern "C" int slb_adamw_step_static(int nseg, float* const* p, const float* con
         Seg& d = segs[s];
         memset(&d, 0, sizeof d);
         d.p = p[s], d.m = m[s], d.v = v[s], d.g[0] = const_cast<float*>(g[s]);
-        d.n = n[s], d.wd = wd ? wd[s] : 0.0f, d.hyper = 0, d.vec = (bits & 15) == 0;
+        d.n = n[s], d.wd = wd ? wd[s] : 0.0f, d.hyper = 0, d.vec = (bits & 15) == 0, d.gscale = 1.0f;
         prefix[s] = (int)tiles;
         tiles += (n[s] + kTile - 1) / kTile;
         if (tiles > 0x7fffffff) return -2;

@@ -29,6 +29,8 @@ int launch_axpy(const float* x, float* y, int64_t n, float alpha, cudaStream_t s
 int launch_fill(float* p, int64_t n, float value, cudaStream_t st);
 // Fixed-shape sum of squares: `blocks` double partials into `partials` (block b sums a fixed contiguous slice,
 // threads and warps combine in a fixed tree), so the result does not depend on scheduling.
+// Sum of squares of nslices tensor slices, one double partial per slice.
+int launch_sumsq_slices(int nslices, const SumsqSlice* slices, double* partials, int blocks, cudaStream_t st);
 int launch_sumsq_partials(const float* x, int64_t n, double* partials, int blocks, cudaStream_t st);
 
 }  // namespace slb

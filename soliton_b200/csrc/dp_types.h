@@ -34,7 +34,17 @@ constexpr size_t kTilePrefixOff = kFlagOff + kFlagBytes;        // (kMaxSegs + 1
 constexpr size_t kSegOff = kTilePrefixOff + 32768;              // kMaxSegs segments
 constexpr size_t kPartialOff = kSegOff + size_t(kMaxSegs) * 112;  // kSumsqBlocks doubles (sum-of-squares partials)
 constexpr int kSumsqBlocks = 1024;
-static_assert(kPartialOff + kSumsqBlocks * 8 <= kCtlBytes, "control area layout");
+// Batched sum of squares over many tensors: tensors are cut into slices of kSumsqSlice floats, one partial each.
+constexpr int kSumsqSlice = 65536;
+constexpr int kMaxSumsqSlices = 16384;
+constexpr size_t kSliceTableOff = kPartialOff + size_t(kSumsqBlocks) * 8;          // kMaxSumsqSlices x {ptr, n}
+constexpr size_t kSlicePartialOff = kSliceTableOff + size_t(kMaxSumsqSlices) * 16;  // kMaxSumsqSlices doubles
+static_assert(kSlicePartialOff + size_t(kMaxSumsqSlices) * 8 <= kCtlBytes, "control area layout");
+
+struct SumsqSlice {      // one slice of one tensor
+    const float* x;
+    int64_t n;
+};
 
 struct Hyper {  // one AdamW hyperparameter set of a step (core/cuda/kernels.cu:251-254 computes bc1, bc2 on the host)
     double bc1, bc2;        // 1 - b1^step, 1 - b2^step, in double
@@ -52,7 +62,8 @@ struct alignas(16) Seg {
     float wd;               // weight decay of this tensor (python/soliton/optim.py:23)
     int hyper;              // index into the launch's Hyper sets
     int vec;                // 1 when every pointer above is 16-byte aligned (128-bit path), else scalar path
-    int pad;
+    float gscale;           // factor applied to the gradient before the update and stored back with it (gradient
+                            // clipping, python/soliton/optim.py:35-38); 1 = gradient used and left as it is
 };
 static_assert(sizeof(Seg) == 112, "segment layout");
 

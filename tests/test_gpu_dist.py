@@ -40,7 +40,7 @@ def params_for(shapes):
     return [(rng.standard_normal(s) * 0.02).astype(np.float32) for s in shapes]
 
 
-def worker(rank, world, init_file, outdir, case, steps, with_ref):
+def worker(rank, world, init_file, outdir, case, steps, with_ref, clip=0.0):
     try:
         import ctypes as C
         from soliton_b200 import distributed, tensor as T
@@ -50,7 +50,7 @@ def worker(rank, world, init_file, outdir, case, steps, with_ref):
         distributed.init(rank, world, init_file, timeout=120)
         params = [T.tensor(a, "cuda") for a in params_for(shapes)]
         opt = AdamW(params, lr=H["lr"], betas=(H["b1"], H["b2"]), eps=H["eps"], weight_decay=H["wd"])
-        modes, launches = [], []
+        modes, launches, norms = [], [], []
         ref_state = None
         if with_ref:
             from oracle import build as obuild
@@ -94,13 +94,16 @@ def worker(rank, world, init_file, outdir, case, steps, with_ref):
                 last_rg = rg
             before = counter("launches")
             distributed.all_reduce_grads(opt.params)
+            if clip:
+                from soliton_b200.optim import clip_grad_norm
+                norms.append(clip_grad_norm(opt.params, clip))
             opt.step()
             T.synchronize()
             launches.append(counter("launches") - before)
             modes.append(counter("last_mode"))
             last_g = [p.grad.numpy() for p in params]
             opt.zero_grad()
-        out = {"modes": np.array(modes), "launches": np.array(launches)}
+        out = {"modes": np.array(modes), "launches": np.array(launches), "norms": np.array(norms)}
         for i, (p, (m, v)) in enumerate(zip(params, opt.state)):
             out[f"p{i}"], out[f"m{i}"], out[f"v{i}"], out[f"g{i}"] = p.numpy(), m.numpy(), v.numpy(), last_g[i]
         if with_ref:
@@ -117,11 +120,11 @@ def worker(rank, world, init_file, outdir, case, steps, with_ref):
         raise
 
 
-def run_ranks(world, case, steps, with_ref):
+def run_ranks(world, case, steps, with_ref, clip=0.0):
     outdir = tempfile.mkdtemp()
     init_file = os.path.join(outdir, "group_id")
     ctx = mp.get_context("spawn")
-    procs = [ctx.Process(target=worker, args=(r, world, init_file, outdir, case, steps, with_ref)) for r in range(world)]
+    procs = [ctx.Process(target=worker, args=(r, world, init_file, outdir, case, steps, with_ref, clip)) for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:
@@ -163,6 +166,38 @@ def test_ranks_match_oracle_bit_for_bit_and_each_other(cuda, world, case):
             np.testing.assert_array_equal(res[r][f"g{i}"].ravel(), means[i])   # p.grad holds the mean afterwards
             np.testing.assert_array_equal(res[r][f"p{i}"].ravel(), state[i][0])
             np.testing.assert_array_equal(res[r][f"m{i}"].ravel(), state[i][1])
+            np.testing.assert_array_equal(res[r][f"v{i}"].ravel(), state[i][2])
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_clipped_step_matches_oracle_and_is_three_launches(cuda, world):
+    """all_reduce_grads -> clip_grad_norm -> step, as examples/gpt2.py:92-94 of the reference runs it."""
+    if n_gpus() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import math
+    steps, clip, case = 2, 0.01, "large"
+    res = run_ranks(world, case, steps, with_ref=False, clip=clip)
+    shapes = CASES[case]
+    state = [[a.ravel().copy(), np.zeros(a.size, np.float32), np.zeros(a.size, np.float32)] for a in params_for(shapes)]
+    for step in range(1, steps + 1):
+        per_rank = [grads_for(r, step, shapes) for r in range(world)]
+        means = [pyoracle.mean_ranks([per_rank[r][i].ravel() for r in range(world)]) for i in range(len(shapes))]
+        norm = math.sqrt(sum(pyoracle.sumsq(g) for g in means))
+        for r in range(world):
+            assert res[r]["norms"][step - 1] == pytest.approx(norm, rel=1e-12)
+            assert res[r]["norms"][step - 1] == res[0]["norms"][step - 1]   # every rank computes the same norm bits
+        dev_norm = float(res[0]["norms"][step - 1])
+        if dev_norm > clip:
+            for g in means:
+                pyoracle.scale(g, g, clip / (dev_norm + 1e-6))
+        for i, s in enumerate(shapes):
+            pyoracle.adamw(state[i][0], means[i], state[i][1], state[i][2], H["lr"], H["b1"], H["b2"], H["eps"],
+                           H["wd"] if len(s) >= 2 else 0.0, step, fma=True)
+    for r in range(world):
+        assert list(res[r]["launches"]) == [3] * steps   # all-reduce, batched sumsq, AdamW with the scale folded in
+        for i in range(len(shapes)):
+            np.testing.assert_array_equal(res[r][f"g{i}"].ravel(), means[i])
+            np.testing.assert_array_equal(res[r][f"p{i}"].ravel(), state[i][0])
             np.testing.assert_array_equal(res[r][f"v{i}"].ravel(), state[i][2])
 
 
