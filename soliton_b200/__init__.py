@@ -6,7 +6,7 @@ Submodules load on first use, so that `python -m soliton_b200.build` works befor
 """
 import importlib
 
-_SUBMODULES = ("build", "distributed", "optim", "tensor", "workload", "_C")
+_SUBMODULES = ("arena", "build", "distributed", "optim", "tensor", "workload", "_C")
 
 
 def __getattr__(name):

@@ -40,7 +40,7 @@ def params_for(shapes):
     return [(rng.standard_normal(s) * 0.02).astype(np.float32) for s in shapes]
 
 
-def worker(rank, world, init_file, outdir, case, steps, with_ref, clip=0.0):
+def worker(rank, world, init_file, outdir, case, steps, with_ref, clip=0.0, use_arena=False):
     try:
         import ctypes as C
         from soliton_b200 import distributed, tensor as T
@@ -48,6 +48,24 @@ def worker(rank, world, init_file, outdir, case, steps, with_ref, clip=0.0):
         from soliton_b200.optim import AdamW
         shapes = CASES[case]
         distributed.init(rank, world, init_file, timeout=120)
+        if use_arena:
+            # plan on meta exactly what this worker allocates below, then serve it from one device allocation:
+            # every rank's gradients then sit at the same offsets of a single IPC-exported block
+            from soliton_b200 import arena
+
+            def dry(dev):
+                ps = [T.empty(s, dev) for s in shapes]
+                o = AdamW(ps)
+                for _ in range(steps):
+                    arena.mark(dev)
+                    gs = [T.empty(s, dev) for s in shapes]
+                    del gs
+                return ps, o
+
+            plan = arena.plan(dry)
+            reserved0 = T.memory_stats("cuda")["reserved"]
+            arena.install(plan, "cuda")
+            assert T.memory_stats("cuda")["reserved"] - reserved0 == plan.bytes
         params = [T.tensor(a, "cuda") for a in params_for(shapes)]
         opt = AdamW(params, lr=H["lr"], betas=(H["b1"], H["b2"]), eps=H["eps"], weight_decay=H["wd"])
         modes, launches, norms = [], [], []
@@ -77,6 +95,8 @@ def worker(rank, world, init_file, outdir, case, steps, with_ref, clip=0.0):
         last_g = None
         for step in range(1, steps + 1):
             gs = grads_for(rank, step, shapes)
+            if use_arena:
+                arena.mark("cuda")
             for p, g in zip(params, gs):
                 p.grad = T.tensor(g, "cuda")
             if with_ref:  # the reference path on copies of the same gradients: grouped ncclAvg, then k_adamw per tensor
@@ -111,6 +131,8 @@ def worker(rank, world, init_file, outdir, case, steps, with_ref, clip=0.0):
                 out[f"rp{i}"], out[f"rm{i}"], out[f"rv{i}"] = rp.numpy(), rm.numpy(), rv.numpy()
                 out[f"rg{i}"] = last_rg[i].numpy()
             R.sl_cuda_nccl_destroy()
+        if use_arena:
+            arena.check("cuda")
         np.savez(os.path.join(outdir, f"rank{rank}.npz"), **out)
         distributed.destroy()
     except BaseException as e:  # the parent reads the failure instead of waiting for a file that never comes
@@ -120,11 +142,11 @@ def worker(rank, world, init_file, outdir, case, steps, with_ref, clip=0.0):
         raise
 
 
-def run_ranks(world, case, steps, with_ref, clip=0.0):
+def run_ranks(world, case, steps, with_ref, clip=0.0, use_arena=False):
     outdir = tempfile.mkdtemp()
     init_file = os.path.join(outdir, "group_id")
     ctx = mp.get_context("spawn")
-    procs = [ctx.Process(target=worker, args=(r, world, init_file, outdir, case, steps, with_ref, clip)) for r in range(world)]
+    procs = [ctx.Process(target=worker, args=(r, world, init_file, outdir, case, steps, with_ref, clip, use_arena)) for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:
@@ -166,6 +188,22 @@ def test_ranks_match_oracle_bit_for_bit_and_each_other(cuda, world, case):
             np.testing.assert_array_equal(res[r][f"g{i}"].ravel(), means[i])   # p.grad holds the mean afterwards
             np.testing.assert_array_equal(res[r][f"p{i}"].ravel(), state[i][0])
             np.testing.assert_array_equal(res[r][f"m{i}"].ravel(), state[i][1])
+            np.testing.assert_array_equal(res[r][f"v{i}"].ravel(), state[i][2])
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_arena_mode_one_exported_block_per_rank(cuda, world):
+    """Allocator mode must not change a bit (tests/test_arena.py:48-50 of the reference), also across ranks."""
+    if n_gpus() < world:
+        pytest.skip(f"needs {world} GPUs")
+    steps = 3
+    res = run_ranks(world, "large", steps, with_ref=False, use_arena=True)
+    state, means = oracle_run(world, "large", steps)
+    for r in range(world):
+        assert list(res[r]["launches"]) == [1] * steps
+        for i in range(len(CASES["large"])):
+            np.testing.assert_array_equal(res[r][f"g{i}"].ravel(), means[i])
+            np.testing.assert_array_equal(res[r][f"p{i}"].ravel(), state[i][0])
             np.testing.assert_array_equal(res[r][f"v{i}"].ravel(), state[i][2])
 
 

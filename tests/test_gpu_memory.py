@@ -56,3 +56,45 @@ def test_steps_take_nothing_from_the_pool(cuda):
     T.synchronize()
     after = T.memory_stats("cuda")
     assert after == before
+
+
+def run_with_marks(device, values, steps=3):
+    """The step loop with a mark at every step boundary, as the reference's trainer runs it (examples/gpt2.py:108)."""
+    from soliton_b200 import arena
+    rng = np.random.default_rng(1)
+    params = [T.tensor(a, device) for a in values]
+    opt = AdamW(params, lr=1e-3)
+    for _ in range(steps):
+        arena.mark(device)
+        for p in params:
+            g = rng.standard_normal(p.shape, dtype=np.float32)
+            p.grad = T.empty(p.shape, device) if device == "meta" else T.tensor(g, device)
+        distributed.all_reduce_grads(opt.params)
+        opt.step()
+        opt.zero_grad()
+    if device == "cuda":
+        T.synchronize()
+    return params, opt
+
+
+def test_arena_run_is_bit_equal_to_pool_run_and_its_size_is_predicted(cuda):
+    # tests/test_arena.py:29-50 of the reference, for this path: allocator mode must not change a bit
+    from soliton_b200 import arena
+    rng = np.random.default_rng(0)
+    values = [rng.standard_normal(s, dtype=np.float32) * 0.02 for s in SHAPES]
+    params, opt = run_with_marks("cuda", values)
+    want = [p.numpy() for p in params] + [m.numpy() for m, _ in opt.state]
+    del params, opt
+    T.empty_cache("cuda")
+    plan = arena.plan(lambda dev: run_with_marks(dev, values))
+    before = T.memory_stats("cuda")["reserved"]
+    arena.install(plan, "cuda")
+    assert T.memory_stats("cuda")["reserved"] - before == plan.bytes      # 0 bytes of prediction error
+    params, opt = run_with_marks("cuda", values, steps=3)
+    arena.check("cuda")
+    got = [p.numpy() for p in params] + [m.numpy() for m, _ in opt.state]
+    for a, b in zip(got, want):
+        np.testing.assert_array_equal(a, b)
+    arena.off("cuda")
+    del params, opt
+    assert T.memory_stats("cuda")["reserved"] == before
