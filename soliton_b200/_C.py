@@ -1,85 +1,71 @@
-"""ctypes bindings to libsoliton_b200.so.
+"""ctypes binding of libsoliton_b200.so, generated from the C header.
 
-Mirrors python/soliton/_C.py:5-70 for the symbols of the data-parallel optimizer path: the same names, result and
-argument types, resolved eagerly at import so that a missing symbol fails here and not in the middle of a step.
-There is no fallback: if the library is not built, importing this module raises.
+`include/soliton_b200.h` is the single statement of the ABI; this module reads its declarations and derives the
+ctypes signature of every function from them, so binding and header cannot drift apart. Every declared symbol is
+resolved when the module is imported: a library that lacks one fails here and not in the middle of a step (the
+reference binds eagerly too, python/soliton/_C.py:68-70). There is no fallback: without the built library the import
+raises.
 """
-import ctypes as C
+import ctypes
 import os
+import re
 
-_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libsoliton_b200.so")
-if not os.path.exists(_PATH):
-    raise ImportError(f"soliton_b200: {_PATH} is not built; run `python -m soliton_b200.build` (needs nvcc)")
-lib = C.CDLL(_PATH)
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "libsoliton_b200.so")
+_HEADER = os.path.join(os.path.dirname(_HERE), "include", "soliton_b200.h")
 
-P, L, I, F, D, S = C.c_void_p, C.c_int64, C.c_int, C.c_float, C.c_double, C.c_size_t
-LP = C.POINTER(C.c_int64)
-PP = C.POINTER(C.c_void_p)
+if not os.path.exists(_LIB_PATH):
+    raise ImportError(f"soliton_b200: {_LIB_PATH} is not built; run `python -m soliton_b200.build` (needs nvcc)")
+lib = ctypes.CDLL(_LIB_PATH)
 
-# Subset of python/soliton/_C.py:11-67 that lies on the path or serves its callers; identical signatures.
-_SIGS = {
-    "sl_alloc": (P, [I, S]),
-    "sl_free": (None, [I, P, S]),
-    "sl_stats": (None, [I, LP]),
-    "sl_reset_stats": (None, [I]),
-    "sl_empty_cache": (None, [I]),
-    "sl_set_limit": (None, [I, L]),
-    "sl_record_start": (None, [I]),
-    "sl_record_stop": (None, [I]),
-    "sl_record_mark": (None, [I]),
-    "sl_record_count": (L, [I]),
-    "sl_record_body": (L, [I]),
-    "sl_record_get": (None, [I, LP, LP, LP]),
-    "sl_arena_install": (I, [I, LP, LP, L, L, L]),
-    "sl_arena_diverged": (I, [I]),
-    "sl_arena_off": (None, [I]),
-    "sl_init_device": (I, [I, I]),
-    "sl_cuda_count": (I, []),
-    "sl_check": (I, [I]),
-    "sl_sync": (None, [I]),
-    "sl_mem_info": (None, [C.POINTER(S), C.POINTER(S)]),
-    "sl_from_host": (None, [I, P, P, S]),
-    "sl_to_host": (None, [I, P, P, S]),
-    "sl_copy": (None, [I, P, P, S]),
-    "sl_fill": (None, [I, P, L, F]),
-    "sl_axpy": (None, [I, P, P, L, F]),
-    "sl_scale": (None, [I, P, P, L, F]),
-    "sl_sumsq": (D, [I, P, L]),
-    "sl_adamw": (None, [I, P, P, P, P, L, F, F, F, F, F, I]),
-    "sl_dist_unique_id": (I, [C.c_char_p]),
-    "sl_dist_init": (I, [I, I, C.c_char_p]),
-    "sl_dist_group": (I, [I, I]),
-    "sl_dist_allreduce_mean": (I, [I, P, L]),
-    "sl_dist_destroy": (None, []),
-    # backend level (core/soliton/api.d:47-48,58-62)
-    "sl_cuda_adamw": (None, [P, P, P, P, L, F, F, F, F, F, I]),
-    "sl_cuda_nccl_unique_id": (I, [C.c_char_p]),
-    "sl_cuda_nccl_init": (I, [I, I, C.c_char_p]),
-    "sl_cuda_nccl_group": (I, [I]),
-    "sl_cuda_nccl_allreduce_mean": (I, [P, L]),
-    "sl_cuda_nccl_destroy": (None, []),
-    "sl_cuda_dp_set_workspace": (I, [P, S]),
-    # additions of this library
-    "slb_workspace_bytes": (S, []),
-    "slb_set_option": (I, [C.c_char_p, L]),
-    "slb_get_counter": (L, [C.c_char_p]),
-    "slb_flush": (None, []),
-    "slb_clear_error": (None, []),
-    "slb_tile_count": (L, [LP, I]),
-    "slb_run_range": (None, [L, I, I, I, I, LP, LP]),
-    "slb_adamw_step_static": (I, [I, PP, PP, PP, PP, LP, C.POINTER(F), F, F, F, F, I]),
-    "slb_sim_step": (I, [I, I, LP, PP, PP, PP, PP, C.POINTER(F), F, F, F, F, I, I, I, I, L, C.c_uint, C.POINTER(I)]),
-    "slb_rdv_selftest": (I, [C.c_char_p, I, I, I]),
-    "slb_rdv_create_id": (I, [C.c_char_p]),
+_SCALARS = {
+    "void": None, "int": ctypes.c_int, "unsigned": ctypes.c_uint, "float": ctypes.c_float, "double": ctypes.c_double,
+    "int64_t": ctypes.c_int64, "size_t": ctypes.c_size_t,
 }
-for _name, (_res, _args) in _SIGS.items():
+
+
+def _ctype(decl):
+    """C type text of a parameter or result -> ctypes type. Strings travel as c_char_p; every other pointer as
+    c_void_p, which takes device addresses (ints), ctypes arrays and byref() alike."""
+    words = [w for w in re.sub(r"\bconst\b", " ", decl).replace("*", " * ").split()]
+    stars = words.count("*")
+    base = [w for w in words if w != "*"]
+    if stars:
+        return ctypes.c_char_p if base[:1] == ["char"] else ctypes.c_void_p
+    return _SCALARS[base[0]]
+
+
+def _declarations(text):
+    """(name, result type text, [parameter type texts]) of every function declared in the header."""
+    text = re.sub(r"/\*.*?\*/", " ", text, flags=re.S)
+    text = re.sub(r"^\s*#.*$", " ", text, flags=re.M)
+    for m in re.finditer(r"([A-Za-z_][\w\s\*]*?)\b(slb?_\w+)\s*\(([^)]*)\)\s*;", text):
+        result, name, params = m.group(1).strip(), m.group(2), m.group(3).strip()
+        if result.startswith("extern"):
+            continue
+        args = []
+        if params and params != "void":
+            for p in params.split(","):
+                p = p.strip()
+                # drop the parameter name: the last identifier, unless the parameter is a bare type
+                m2 = re.match(r"^(.*?[\*\s])([A-Za-z_]\w*)$", p)
+                args.append(m2.group(1).strip() if m2 and m2.group(1).strip() else p)
+        yield name, result, args
+
+
+_SIGS = {}
+with open(_HEADER) as _f:
+    for _name, _result, _args in _declarations(_f.read()):
+        _SIGS[_name] = (_ctype(_result), [_ctype(a) for a in _args])
+for _name, (_res, _argtypes) in _SIGS.items():
     _fn = getattr(lib, _name)
-    _fn.restype, _fn.argtypes = _res, _args
+    _fn.restype, _fn.argtypes = _res, _argtypes
 
 
-def longs(xs):
-    xs = list(xs)
-    return (C.c_int64 * max(len(xs), 1))(*xs)
+def longs(values):
+    """A C array of int64 (at least one element, so that an empty list still yields a valid pointer)."""
+    values = list(values)
+    return (ctypes.c_int64 * max(len(values), 1))(*values)
 
 
 def set_option(name, value):
