@@ -221,6 +221,7 @@ int slb_rdv_selftest(const char* id128, int rank, int world, int rounds) {
     if (r.open(id128, rank, world, wait_s) != 0) return -1;
     int rc = 0;
     if (r.stage_barrier(1, wait_s) != 0) rc = -2;
+    if (rc == 0) r.unlink_now();
     // Round k: rank q publishes nseg = 3 + (k / 2) % 2 segments {export q, offset 1000 q + 16 (k / 2) + s, n = 7 s + 1},
     // so tables change every second round and the unchanged rounds must not bump the version.
     uint64_t last_version[kRdvMaxWorld] = {0};

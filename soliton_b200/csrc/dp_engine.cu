@@ -468,6 +468,7 @@ int Engine::dist_init(int rank, int world, const char* id) {
     }
     if (!ok) rdv_.fail();
     ok = ok && rdv_.stage_barrier(2, opt.host_timeout_s) == 0;
+    if (ok) rdv_.unlink_now();  // everybody has the file mapped: its name is not needed any more
     if (!ok) {
         cudaGetLastError();
         close_peer_maps();

@@ -92,6 +92,10 @@ void Rendezvous::close() {
     if (owner_) unlink(path_);
 }
 
+void Rendezvous::unlink_now() {
+    if (shm_ && owner_) unlink(path_);
+}
+
 void Rendezvous::fail() {
     if (shm_) self().failed.store(1, std::memory_order_release);
 }

@@ -64,6 +64,9 @@ public:
 
     int open(const char id[kIdBytes], int rank, int world, double timeout_s);
     void close();
+    // Rank 0, once every rank has mapped the file: remove its name. The mapping stays valid for all of them, and
+    // nothing is left behind in the file system if the job dies later.
+    void unlink_now();
     bool is_open() const { return shm_ != nullptr; }
 
     int rank() const { return rank_; }
