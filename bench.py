@@ -176,7 +176,7 @@ def run_reference(args, rank, world):
     line = {
         "impl": "reference", "metric": "fused_allreduce_adamw_algorithmic_GBps", "value": value, "unit": "GB/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32 (p update in f64)", "data": "synthetic",
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": name, "params_per_rank": total, "world": world},
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": "port",
                          "sample": f"first {n} parameters per step, {args.steps} steps, one thread per rank "
@@ -336,10 +336,11 @@ def run_ours(args, rank, local_rank, world):
     line = {
         "metric": "fused_allreduce_adamw_algorithmic_GBps", "value": value, "unit": "GB/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32 (p update in f64)", "data": "synthetic",
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": name, "params_per_rank": P, "world": world, "l2": "inputs larger than L2, no flush",
                    "exchange": {0: "none", 1: "one-shot", 2: "two-shot"}[mode], "blocks_per_rank": blocks,
                    "optimizer": "none (--bare)" if args.bare else "AdamW",
+                   "arithmetic": "gradient mean, m, v in f32; parameter update in f64, rounded to f32 once",
                    "e2e_copies": "h2d: this step's gradients from pinned memory; d2h: updated parameters"},
         "roofline": roof,
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": 4 * P, "d2h_bytes_per_step": 4 * P,
