@@ -318,7 +318,7 @@ def run_ours(args, rank, local_rank, world):
     nvl_bytes = 8.0 * P * (world - 1) / world
     t_nvl = nvl_bytes / (NVLINK_GBS * 1e9)
     per_launch_ms = total_ms / max(launches, 1)
-    use_step = args.pipeline == 1 or (args.pipeline < 0 and world == 2)
+    use_step = args.pipeline == 1
     base = "k_step" if use_step else "k_twoshot"
     kernel = {0: f"{base}<1,adam>", 1: f"k_oneshot<{world},adam>", 2: f"{base}<{world},adam>"}[mode]
     traffic = NCU_DRAM_BYTES_PER_PARAM.get(world)

@@ -68,6 +68,37 @@ __device__ __forceinline__ float ld_sys1(const float* p) {
     asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
     return v;
 }
+// 256-bit accesses (sm_100): eight floats per thread and instruction, half as many memory instructions and requests
+// for the same bytes.
+struct alignas(32) float8 {
+    float4 lo, hi;
+};
+__device__ __forceinline__ float8 ld_sys8(const float* p) {
+    float8 v;
+    asm volatile("ld.relaxed.sys.global.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=f"(v.lo.x), "=f"(v.lo.y), "=f"(v.lo.z), "=f"(v.lo.w), "=f"(v.hi.x), "=f"(v.hi.y), "=f"(v.hi.z), "=f"(v.hi.w)
+                 : "l"(p)
+                 : "memory");
+    return v;
+}
+__device__ __forceinline__ float8 ld_stream8(const float* p) {
+    float8 v;
+    asm volatile("ld.global.cs.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=f"(v.lo.x), "=f"(v.lo.y), "=f"(v.lo.z), "=f"(v.lo.w), "=f"(v.hi.x), "=f"(v.hi.y), "=f"(v.hi.z), "=f"(v.hi.w)
+                 : "l"(p)
+                 : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_stream8(float* p, const float8& v) {
+    asm volatile("st.global.cs.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "f"(v.lo.x), "f"(v.lo.y), "f"(v.lo.z),
+                 "f"(v.lo.w), "f"(v.hi.x), "f"(v.hi.y), "f"(v.hi.z), "f"(v.hi.w)
+                 : "memory");
+}
+__device__ __forceinline__ void st_plain8(float* p, const float8& v) {
+    asm volatile("st.global.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "f"(v.lo.x), "f"(v.lo.y), "f"(v.lo.z),
+                 "f"(v.lo.w), "f"(v.hi.x), "f"(v.hi.y), "f"(v.hi.z), "f"(v.hi.w)
+                 : "memory");
+}
 // Local tensors that are read once and written once per step: streaming (evict-first) accesses.
 __device__ __forceinline__ float4 ld_stream4(const float* p) { return __ldcs(reinterpret_cast<const float4*>(p)); }
 __device__ __forceinline__ void st_stream4(float* p, float4 v) { __stcs(reinterpret_cast<float4*>(p), v); }
@@ -201,65 +232,55 @@ __device__ __forceinline__ void do_tile(const SegView<W>& s, const LaunchArgs& a
     const int slot = a.stage_slot_floats;
     const Hyper& h = a.hp[s.hyper];
     const bool adam = ADAM && s.p != nullptr;
-    constexpr int U = kTile / (4 * kThreads);
-
     if (s.vec && cnt == kTile) {
-        float4 gv[U][W], pv[U], mv[U], vv[U];
-        // every load of the tile is issued before the first use
-#pragma unroll
-        for (int u = 0; u < U; u++) {
-            const int e = (tid + u * kThreads) * 4;
-            const int64_t off = base + e;
-            if (MODE == REDUCE_OWN) {
-                if (W == 1) {
-                    gv[u][0] = ld_stream4(s.gme + off);
-                } else {
-#pragma unroll
-                    for (int r = 0; r < W; r++) gv[u][r] = ld_sys4(s.g[r] + off);
-                }
-            } else if (MODE == GATHER) {
-                gv[u][0] = ld_sys4(s.gsrc + off);
-            } else if (MODE == REDUCE_STAGED) {
-#pragma unroll
-                for (int r = 0; r < W; r++)
-                    gv[u][r] = r == me ? ld_sys4(s.gme + off) : ld_sys4(stage + (size_t)r * slot + (size_t)t * kTile + e);
+        // one 256-bit access per stream and thread; every load of the tile is issued before the first use
+        static_assert(kTile == 8 * kThreads, "one float8 per thread and stream");
+        const int e = tid * 8;
+        const int64_t off = base + e;
+        float8 gv[W], pv, mv, vv;
+        if (MODE == REDUCE_OWN) {
+            if (W == 1) {
+                gv[0] = ld_stream8(s.gme + off);
             } else {
-                gv[u][0] = ld_stream4(s.gme + off);
+#pragma unroll
+                for (int r = 0; r < W; r++) gv[r] = ld_sys8(s.g[r] + off);
             }
-            if (MODE != PUSH && adam) {
-                pv[u] = ld_stream4(s.p + off);
-                mv[u] = ld_stream4(s.m + off);
-                vv[u] = ld_stream4(s.v + off);
-            }
+        } else if (MODE == GATHER) {
+            gv[0] = ld_sys8(s.gsrc + off);
+        } else if (MODE == REDUCE_STAGED) {
+#pragma unroll
+            for (int r = 0; r < W; r++)
+                gv[r] = r == me ? ld_sys8(s.gme + off) : ld_sys8(stage + (size_t)r * slot + (size_t)t * kTile + e);
+        } else {
+            gv[0] = ld_stream8(s.gme + off);
         }
+        if (MODE != PUSH && adam) {
+            pv = ld_stream8(s.p + off);
+            mv = ld_stream8(s.m + off);
+            vv = ld_stream8(s.v + off);
+        }
+        if (MODE == PUSH) {
 #pragma unroll
-        for (int u = 0; u < U; u++) {
-            const int e = (tid + u * kThreads) * 4;
-            const int64_t off = base + e;
-            if (MODE == PUSH) {
-#pragma unroll
-                for (int r = 0; r < W; r++)
-                    if (r != me)
-                        *reinterpret_cast<float4*>(c.stage[r] + stage_off + (size_t)me * slot + (size_t)t * kTile + e) =
-                            gv[u][0];
-                continue;
-            }
-            float4 avg = gv[u][0];
+            for (int r = 0; r < W; r++)
+                if (r != me) st_plain8(c.stage[r] + stage_off + (size_t)me * slot + (size_t)t * kTile + e, gv[0]);
+        } else {
+            float8 avg = gv[0];
             if (MODE != GATHER && W > 1) {
 #pragma unroll
-                for (int r = 1; r < W; r++) avg = add4(avg, gv[u][r]);
-                avg = mul4(avg, a.inv_world);
+                for (int r = 1; r < W; r++) avg.lo = add4(avg.lo, gv[r].lo), avg.hi = add4(avg.hi, gv[r].hi);
+                avg.lo = mul4(avg.lo, a.inv_world), avg.hi = mul4(avg.hi, a.inv_world);
             }
             if (W == 1 && s.gscale != 1.0f) {  // clipped gradient: y = alpha * x in float, kept in place
-                avg = mul4(avg, s.gscale);
-                st_stream4(s.gme + off, avg);
+                avg.lo = mul4(avg.lo, s.gscale), avg.hi = mul4(avg.hi, s.gscale);
+                st_stream8(s.gme + off, avg);
             }
-            if (W > 1) st_stream4(s.gme + off, avg);
+            if (W > 1) st_stream8(s.gme + off, avg);
             if (adam) {
-                adamw_vec(pv[u], avg, mv[u], vv[u], h, s.wd);
-                st_stream4(s.p + off, pv[u]);
-                st_stream4(s.m + off, mv[u]);
-                st_stream4(s.v + off, vv[u]);
+                adamw_vec(pv.lo, avg.lo, mv.lo, vv.lo, h, s.wd);
+                adamw_vec(pv.hi, avg.hi, mv.hi, vv.hi, h, s.wd);
+                st_stream8(s.p + off, pv);
+                st_stream8(s.m + off, mv);
+                st_stream8(s.v + off, vv);
             }
         }
     } else {
@@ -1065,7 +1086,7 @@ extern "C" int slb_adamw_step_static(int nseg, float* const* p, const float* con
         Seg& d = segs[s];
         memset(&d, 0, sizeof d);
         d.p = p[s], d.m = m[s], d.v = v[s], d.g[0] = const_cast<float*>(g[s]);
-        d.n = n[s], d.wd = wd ? wd[s] : 0.0f, d.hyper = 0, d.vec = (bits & 15) == 0, d.gscale = 1.0f;
+        d.n = n[s], d.wd = wd ? wd[s] : 0.0f, d.hyper = 0, d.vec = (bits & 31) == 0, d.gscale = 1.0f;
         prefix[s] = (int)tiles;
         tiles += (n[s] + kTile - 1) / kTile;
         if (tiles > 0x7fffffff) return -2;
