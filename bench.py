@@ -32,7 +32,7 @@ BYTES_PER_PARAM = 28            # algorithmic HBM bytes per parameter per rank
 NVLINK_GBS = 770.0              # measured peer copy bandwidth per direction on this pool (nominal 900)
 FALLBACK_HBM_GBS = 6650.0       # used only when MEASURED_PEAKS.json is absent
 # DRAM bytes per parameter of the dominant kernel from an ncu capture (profiles/), per world size; None = not captured
-NCU_DRAM_BYTES_PER_PARAM = {1: 27.18}  # profiles/k_twoshot_w1_flat256MiB_ncu.md
+NCU_DRAM_BYTES_PER_PARAM = {1: 27.22}  # profiles/k_twoshot_w1_flat256MiB_ncu.md
 
 
 def parse():

@@ -37,7 +37,7 @@ static void* cuda_raw_alloc(size_t n) {
 }
 static void cuda_raw_free(void* p) { cudaFree(p); }
 
-static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 31) == 0; }  // vector path: 256-bit accesses, so 32 bytes despite the name
+static bool aligned_vec(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 31) == 0; }  // 256-bit accesses
 static bool aligned4(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 3) == 0; }
 
 // Base and size of the device allocation that contains p: the pool's own registry first, the driver otherwise
@@ -287,10 +287,10 @@ static int64_t build_table(const std::vector<StepItem>& items, int world, int ra
         const StepItem& it = items[s];
         Seg& d = segs[s];
         d.p = it.p, d.m = it.m, d.v = it.v, d.n = it.n, d.wd = it.wd, d.hyper = it.hyper, d.gscale = it.gscale;
-        bool vec = aligned16(it.g) && (!it.p || (aligned16(it.p) && aligned16(it.m) && aligned16(it.v)));
+        bool vec = aligned_vec(it.g) && (!it.p || (aligned_vec(it.p) && aligned_vec(it.m) && aligned_vec(it.v)));
         for (int r = 0; r < world; r++) {
             d.g[r] = (world == 1 || r == rank) ? it.g : peer_g[r][s];
-            vec = vec && aligned16(d.g[r]);
+            vec = vec && aligned_vec(d.g[r]);
         }
         d.vec = vec ? 1 : 0;
         if (it.p) *any_adam = true;

@@ -4,8 +4,8 @@
 // k_adamw launch per tensor (core/cuda/kernels.cu:242-254).
 //
 // The path is bandwidth-bound (28 algorithmic HBM bytes per parameter, no contraction), so the kernels are built
-// around memory traffic: 128-bit coalesced accesses, every thread issuing all loads of a tile before it touches
-// the data (2 x (3 + ranks) independent 16-byte loads per thread), streaming cache hints for local tensors, one
+// around memory traffic: 256-bit coalesced accesses, every thread issuing all loads of a tile before it touches
+// the data (3 + ranks independent 32-byte loads per thread), streaming cache hints for local tensors, one
 // launch for all tensors of a step, and grids sized to the number of blocks that are resident at once.
 // Peer gradients are read and written directly through NVSwitch-mapped pointers; no library collective runs.
 //

@@ -13,8 +13,7 @@ namespace slb {
 
 constexpr int kMaxWorld = 8;        // ranks of one NVSwitch box
 constexpr int kThreads = 256;       // threads per block
-constexpr int kVecPerThread = 2;    // float4 vectors per thread, tensor stream and tile
-constexpr int kTile = 4 * kThreads * kVecPerThread;  // floats per tile: 2048 (8 KiB per tensor stream)
+constexpr int kTile = 8 * kThreads; // floats per tile: 2048 (8 KiB per tensor stream), one 256-bit access per thread
 constexpr int kMaxSegs = 4096;      // segments per step
 constexpr int kMaxHyper = 8;        // distinct hyperparameter sets per step
 constexpr int kFlagBlocks = 1024;   // upper bound on blocks per rank that take part in flag barriers
@@ -61,7 +60,7 @@ struct alignas(16) Seg {
     int64_t n;              // elements
     float wd;               // weight decay of this tensor (python/soliton/optim.py:23)
     int hyper;              // index into the launch's Hyper sets
-    int vec;                // 1 when every pointer above is 16-byte aligned (128-bit path), else scalar path
+    int vec;                // 1 when every pointer above is 32-byte aligned (256-bit path), else scalar path
     float gscale;           // factor applied to the gradient before the update and stored back with it (gradient
                             // clipping, python/soliton/optim.py:35-38); 1 = gradient used and left as it is
 };
