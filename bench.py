@@ -47,6 +47,7 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--mode", type=int, default=0, help="0 auto, 1 one-shot, 2 two-shot")
     ap.add_argument("--blocks-per-sm", type=int, default=0)
+    ap.add_argument("--cyclic", type=int, default=-1)
     ap.add_argument("--sweep", action="store_true", help="bucket-size sweep 4 KB .. 1 GB, one-shot vs two-shot (N >= 2)")
     ap.add_argument("--bare", action="store_true", help="gradient mean only, no optimizer update (link-bound floor)")
     ap.add_argument("--pipeline", type=int, default=-1, help="-1 auto, 1 k_step (shared-memory ring), 0 k_twoshot")
@@ -222,6 +223,8 @@ def run_ours(args, rank, local_rank, world):
         set_option("blocks_per_sm", args.blocks_per_sm)
     if args.pipeline >= 0:
         set_option("pipeline", args.pipeline)
+    if args.cyclic >= 0:
+        set_option("cyclic", args.cyclic)
     if world > 1:
         idt = torch.zeros(128, dtype=torch.uint8, device="cuda")
         if rank == 0:

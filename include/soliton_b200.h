@@ -129,7 +129,8 @@ int sl_cuda_dp_set_workspace(void* p, size_t n);
 /* ------------------------------------------------------------------ 3. slb_*: no counterpart in the reference */
 
 size_t slb_workspace_bytes(void);
-/* Options: "eager" (0/1), "mode" (0 auto, 1 one-shot, 2 two-shot), "blocks_per_sm", "pipeline" (which kernel takes large
+/* Options: "eager" (0/1), "mode" (0 auto, 1 one-shot, 2 two-shot), "blocks_per_sm", "cyclic" (single-rank steps:
+ * blocks take groups of this many tiles round robin; 0 = one contiguous run per block; default 4), "pipeline" (which kernel takes large
  * steps: 1 k_step, the shared-memory ring; 0 k_twoshot, register-staged; -1, the default, the faster per world size), "timeout_ms" (device waits),
  * "host_timeout_ms", "oneshot_max_bytes" (-1: whatever fits the staging slots). Must be set alike on all ranks.
  * Returns 0, or -1 for an unknown name. */

@@ -172,6 +172,7 @@ int slb_set_option(const char* name, int64_t value) {
     else if (!strcmp(name, "mode")) o.mode = (int)value;
     else if (!strcmp(name, "blocks_per_sm")) o.blocks_per_sm = (int)value;
     else if (!strcmp(name, "pipeline")) o.pipeline = (int)value;
+    else if (!strcmp(name, "cyclic")) o.cyclic = (int)value;
     else if (!strcmp(name, "timeout_ms")) o.timeout_ns = (unsigned long long)value * 1000000ull;
     else if (!strcmp(name, "host_timeout_ms")) o.host_timeout_s = (double)value / 1000.0;
     else if (!strcmp(name, "oneshot_max_bytes")) o.oneshot_max_bytes = value;

@@ -397,6 +397,7 @@ int Engine::launch_items(std::vector<StepItem>& items, const std::vector<HyperKe
     a.timeout_ns = opt.timeout_ns;
     a.inv_world = 1.0f / (float)W;
     a.stages = stages;
+    a.cyclic = opt.cyclic;
     for (size_t i = 0; i < hypers.size() && i < (size_t)kMaxHyper; i++) fill_hyper(a.hp[i], hypers[i]);
     last_mode = W == 1 ? 0 : (oneshot ? 1 : 2);
     last_blocks = G;

@@ -398,6 +398,21 @@ __global__ void __launch_bounds__(kThreads, W == 1 ? kLocalBlocksPerSm : 2) k_tw
         post<W>(c, B_START, b, me, a.seq);
         await<W>(c, a, B_START, b, me, -1, ST_TIMEOUT_START, &s_abort);
     }
+    if (W == 1 && a.cyclic > 0) {
+        // single rank, block-cyclic order: block b takes groups b, b + G, ... of `cyclic` consecutive tiles, so that
+        // the resident blocks walk through each tensor stream side by side instead of in G far-apart places
+        const int C = a.cyclic, groups = (T + C - 1) / C;
+        SegView<W> s;
+        s.first_tile = 0, s.end_tile = 0;
+        for (int j = b; j < groups; j += G) {
+            const int t1 = (j + 1) * C < T ? (j + 1) * C : T;
+            for (int t = j * C; t < t1; t++) {
+                if (t >= s.end_tile || t < s.first_tile) load_seg<W>(s, c, s_prefix, t, me, me);
+                do_tile<W, ADAM, REDUCE_OWN>(s, a, c, t, me, nullptr, 0);
+            }
+        }
+        return;
+    }
     {   // own chunk: reduce, scale, update
         const int cb = cut(T, me, W), ce = cut(T, me + 1, W), L = ce - cb;
         if (!s_abort) do_run<W, ADAM, REDUCE_OWN>(a, c, s_prefix, cb + cut(L, b, G), cb + cut(L, b + 1, G), me, me, nullptr, 0);

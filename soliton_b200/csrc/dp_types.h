@@ -97,6 +97,7 @@ struct LaunchArgs {
     unsigned long long timeout_ns;  // bound of every flag wait
     float inv_world;
     int stages;                     // shared-memory pipeline depth of k_step (2..8)
+    int cyclic;                     // single-rank k_twoshot: > 0 = block-cyclic tile order in groups of this many tiles
     Hyper hp[kMaxHyper];
 };
 
