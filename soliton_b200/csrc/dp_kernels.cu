@@ -16,8 +16,12 @@
 //                      With W == 1 this is the plain multi-tensor AdamW step.
 //   k_oneshot<W,ADAM>  for small steps: every rank pushes its gradients into a staging slot on every peer, one
 //                      barrier, then every rank reduces all W copies locally in the same rank order.
+//   k_step<W,ADAM>     the same exchange as k_twoshot with the tiles staged through a shared-memory ring that the
+//                      bulk-copy engine fills and drains (loader thread / compute warps / storer thread) and with
+//                      the mean published slice by slice. Measured slower than k_twoshot at every world size, so
+//                      it only runs when the "pipeline" option asks for it.
 //
-// Both produce the same bits: the sum is ((g0 + g1) + g2) + ... in float, then one multiply by 1/W, whoever
+// All of them produce the same bits: the sum is ((g0 + g1) + g2) + ... in float, then one multiply by 1/W, whoever
 // computes it; so weights stay bit-identical across ranks and across the one-shot/two-shot choice.
 //
 // Synchronisation is per block index: block b of a rank only ever depends on block b of its peers, because the

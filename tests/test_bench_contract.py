@@ -30,6 +30,24 @@ def test_reference_arm_prints_one_contract_line(built):
     assert "workload" in d["config"] and "model" not in d["config"]
 
 
+def test_reference_arm_under_torchrun_only_rank_zero_reports(built):
+    """Launched the way the scaling runs launch it (one process per rank): rank 0 times the host path with one
+    thread per rank, the other ranks leave quietly."""
+    import socket
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                          "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "bench.py"),
+                          "--impl", "reference", "--gpus", "2", "--steps", "2", "--warmup", "1"],
+                         capture_output=True, text=True, timeout=600, cwd=ROOT)
+    assert out.returncode == 0, out.stderr[-2000:]
+    lines = [json.loads(l) for l in out.stdout.splitlines() if l.startswith("{")]
+    assert len(lines) == 1
+    assert lines[0]["n_gpus"] == 2 and lines[0]["cpu_baseline"]["cores"] == 2 and lines[0]["impl"] == "reference"
+
+
 @pytest.mark.gpu
 def test_product_arm_prints_one_contract_line(cuda):
     d = run_bench("--flat", str(64 << 20), "--steps", "5", "--warmup", "3", "--e2e-steps", "1")

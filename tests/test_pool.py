@@ -154,3 +154,50 @@ def test_init_device_reserves_the_same_on_meta_each_time(clean):
     assert after["allocated"] - before["allocated"] == (32 << 20) + lib.slb_workspace_bytes()
     assert lib.slb_workspace_bytes() == 18 << 20
     assert lib.sl_init_device(CPU, 0) == 0
+
+
+@pytest.mark.parametrize("dev", [CPU, META])
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_random_traces_match_the_restated_reference_policy(clean, dev, seed):
+    """Differential test against oracle/pool_model.py (alloc.d restated in Python): every counter after every
+    operation, including reserve-limit refusals, flush-and-retry, cache flushes and statistic resets."""
+    from oracle.pool_model import PoolModel
+    lib = clean
+    rng = np.random.default_rng(seed)
+    base = stats(lib, dev)
+    model = PoolModel()
+    live = []
+    sizes = [int(x) for x in rng.choice([1, 300, 512, 4096, 70000, 1 << 20, (1 << 20) + 5, 3 << 20, 9 << 20], 400)]
+    for step, n in enumerate(sizes):
+        op = rng.random()
+        if op < 0.55 or not live:
+            p, tok = lib.sl_alloc(dev, n), model.alloc(n)
+            assert bool(p) == (tok is not None)
+            if p:
+                live.append((p, tok, n))
+        elif op < 0.9:
+            p, tok, m = live.pop(int(rng.integers(len(live))))
+            lib.sl_free(dev, p, m)
+            model.release(tok, m)
+        elif op < 0.94:
+            lib.sl_empty_cache(dev)
+            model.empty_cache()
+        elif op < 0.97:
+            lib.sl_reset_stats(dev)
+            model.reset_stats()
+            base = dict(base, peak_allocated=base["allocated"], peak_reserved=base["reserved"])
+        else:
+            cap = int(rng.choice([0, 24 << 20, 64 << 20]))
+            lib.sl_set_limit(dev, base["reserved"] + cap if cap else 0)
+            model.limit = cap
+        got, want = stats(lib, dev), model.stats()
+        rel = [got["allocated"] - base["allocated"], got["reserved"] - base["reserved"],
+               got["peak_allocated"] - base["allocated"], got["peak_reserved"] - base["reserved"],
+               got["n_alloc"], got["n_raw"], got["trace"]]
+        # the library's pools already hold the fixed workspaces of earlier tests: compare growth, not totals
+        want[2] = max(want[2], 0)
+        assert rel[0] == want[0] and rel[1] == want[1] and rel[4:] == want[4:], (step, rel, want)
+    for p, tok, m in live:
+        lib.sl_free(dev, p, m)
+    lib.sl_set_limit(dev, 0)
+    lib.sl_empty_cache(dev)
