@@ -192,3 +192,58 @@ def test_scale_axpy_fill_sumsq_next_to_the_path(cuda):
     lib.sl_fill(CUDA, x.ptr, n, 1.5)
     assert (x.get() == 1.5).all()
     check_ok()
+
+
+def test_pending_update_goes_out_before_anything_can_touch_its_memory(cuda):
+    """The recorded (not yet launched) update must behave as if it had run at the call: freeing and reusing the
+    gradient's block, copying the parameter, filling a moment -- each has to see or preserve the right values."""
+    n = 70000
+    p0, g0 = workload.flat_case(n)
+    ref = [p0.copy(), np.zeros(n, np.float32), np.zeros(n, np.float32)]
+    pyoracle.adamw(ref[0], g0, ref[1], ref[2], H["lr"], H["b1"], H["b2"], H["eps"], 0.1, 1, fma=True)
+
+    # (a) the gradient's block is freed and handed out again before any launch was forced
+    p, g, m, v = DevBuf(p0), DevBuf(g0), zeros(n), zeros(n)
+    before = counter("launches")
+    dev_adamw(p, g, m, v, 0.1, 1)
+    assert counter("launches") == before            # recorded only
+    old_ptr = g.ptr
+    g.free()                                         # launches the update, then releases the block
+    assert counter("launches") == before + 1
+    g2 = DevBuf(np.full(n, 123.0, np.float32))       # same size: the pool hands the same block out again
+    assert g2.ptr == old_ptr
+    check_ok()
+    np.testing.assert_array_equal(p.get(), ref[0])
+
+    # (b) a device-to-device copy of the parameter sees the updated values
+    p, g, m, v, q = DevBuf(p0), DevBuf(g0), zeros(n), zeros(n), zeros(n)
+    dev_adamw(p, g, m, v, 0.1, 1)
+    lib.sl_copy(CUDA, q.ptr, p.ptr, 4 * n)
+    np.testing.assert_array_equal(q.get(), ref[0])
+
+    # (c) filling the second moment after the call does not reach back into the update
+    p, g, m, v = DevBuf(p0), DevBuf(g0), zeros(n), zeros(n)
+    dev_adamw(p, g, m, v, 0.1, 1)
+    lib.sl_fill(CUDA, v.ptr, n, 7.0)
+    np.testing.assert_array_equal(p.get(), ref[0])
+    assert (v.get() == 7.0).all()
+    check_ok()
+
+
+def test_eager_option_launches_at_every_call(cuda):
+    n = 3000
+    p0, g0 = workload.flat_case(n)
+    bufs = [(DevBuf(p0), DevBuf(g0), zeros(n), zeros(n)) for _ in range(3)]
+    set_option("eager", 1)
+    try:
+        before = counter("launches")
+        for p, g, m, v in bufs:
+            dev_adamw(p, g, m, v, 0.1, 1)
+        assert counter("launches") == before + 3
+    finally:
+        set_option("eager", 0)
+    check_ok()
+    ref = [p0.copy(), np.zeros(n, np.float32), np.zeros(n, np.float32)]
+    pyoracle.adamw(ref[0], g0, ref[1], ref[2], H["lr"], H["b1"], H["b2"], H["eps"], 0.1, 1, fma=True)
+    for p, g, m, v in bufs:
+        np.testing.assert_array_equal(p.get(), ref[0])
