@@ -129,17 +129,34 @@ int sl_cuda_dp_set_workspace(void* p, size_t n);
 /* ------------------------------------------------------------------ 3. slb_*: no counterpart in the reference */
 
 size_t slb_workspace_bytes(void);
-/* Options: "eager" (0/1), "mode" (0 auto, 1 one-shot, 2 two-shot), "blocks_per_sm", "cyclic" (single-rank steps:
- * blocks take groups of this many tiles round robin; 0 = one contiguous run per block; default 4), "pipeline" (which kernel takes large
- * steps: 1 k_step, the shared-memory ring; 0 k_twoshot, register-staged; -1, the default, the faster per world size), "timeout_ms" (device waits),
+/* Options: "eager" (0/1: launch at every call instead of deferring -- with it a Soliton build needs no slb_flush
+ * hooks at all), "mode" (0 auto, 1 one-shot, 2 two-shot), "blocks_per_sm", "cyclic" (single-rank steps: blocks take
+ * groups of this many tiles round robin; 0 = one contiguous run per block; default 4), "prefetch" (two-shot: peer
+ * loads run a few tiles ahead of the arithmetic; default 1; same bits either way), "stamps" (collective launches
+ * record device times at their phase borders, see slb_read_stamps), "overlap" (1: the path's launches go to a stream
+ * of their own beside the legacy stream, ordered against it by events; default 0), "timeout_ms" (device waits),
  * "host_timeout_ms", "oneshot_max_bytes" (-1: whatever fits the staging slots). Must be set alike on all ranks.
  * Returns 0, or -1 for an unknown name. */
 int slb_set_option(const char* name, int64_t value);
 /* Counters: "launches" (kernels of this library launched so far), "last_mode" (0 local, 1 one-shot, 2 two-shot),
- * "last_blocks", "world", "sm_count". -1 for an unknown name. */
+ * "last_blocks", "world", "sm_count", "pending_frees" (exported allocations this rank has released and still holds
+ * until every peer has closed its mapping). -1 for an unknown name. */
 int64_t slb_get_counter(const char* name);
 /* Launches whatever step is pending without waiting for the device (sl_sync does the same and then waits). */
 void slb_flush(void);
+/* Copies beside the path, for callers that feed the step bucket by bucket (python/soliton/tensor.py:427-471 makes
+ * gradients final in reverse layer order): k buffers per call between PINNED host memory and device memory, on
+ * streams of their own (one per direction). Ordering is by address: an upload waits for launched work that still
+ * reads or writes its destination, a launch waits for uploads into its tensors and for downloads that still read
+ * them, a download waits for the launch that writes its source. Blocking entry points (sl_to_host, sl_sync, ...)
+ * wait as well. slb_wait_copies blocks the host until both copy streams are idle. 0 or -1. */
+int slb_from_host_async(int k, void* const* dst, const void* const* src, const size_t* bytes);
+int slb_to_host_async(int k, void* const* dst, const void* const* src, const size_t* bytes);
+int slb_wait_copies(void);
+/* With option "stamps": device times (globaltimer, ns) that block 0 of the last collective launch took at its phase
+ * borders: start, every peer present, own chunk reduced, all chunks gathered, every peer done. Waits for the
+ * device. 0 or -1. */
+int slb_read_stamps(uint64_t* out5);
 /* Clears the sticky error (after a test provoked one on purpose). */
 void slb_clear_error(void);
 /* The partition the kernels use: tiles of the step, and the tile range [*begin, *end) that block `block` of
@@ -159,14 +176,24 @@ int slb_adamw_step_static(int nseg, float* const* p, const float* const* g, floa
 /* Test hook: `world` ranks emulated on one GPU by one cooperative launch (blocks of all ranks resident together).
  * Pointer arrays are indexed [rank * nseg + segment]; p/m/v may be NULL when adam = 0. mode: 0 auto, 1 one-shot,
  * 2 two-shot. active_mask: bit r set = rank r takes part (a missing rank makes the others' waits run out).
- * status_out[world] receives each rank's device status (0, or 21/22/23). Returns 0 or a negative code. */
+ * status_out[world] receives each rank's device status (0, or 21/22/23). sumsq_out (NULL, or world x nseg doubles;
+ * two-shot without an optimizer only): per rank and tensor, the sum of squares of the mean as the launch's piece
+ * table on that rank gives it. Returns 0 or a negative code. */
 int slb_sim_step(int world, int nseg, const int64_t* n, float* const* p, float* const* g, float* const* m,
                  float* const* v, const float* wd, float lr, float b1, float b2, float eps, int step, int adam,
-                 int mode, int blocks_per_rank, int64_t timeout_ms, unsigned active_mask, int* status_out);
+                 int mode, int blocks_per_rank, int64_t timeout_ms, unsigned active_mask, int* status_out,
+                 double* sumsq_out);
 /* Test hook: runs the host rendezvous protocol (no CUDA) as rank `rank` of `world` for `rounds` collectives with
  * synthetic tables and checks what it reads from the peers. 0 when everything matched. */
 int slb_rdv_selftest(const char* id128, int rank, int world, int rounds);
 int slb_rdv_create_id(char* out128);
+/* Test hook: the life cycle of export slots (published, freed by the owner, let go by every peer, reused) driven
+ * by `world` processes without CUDA, `cycles` x `per_cycle` fake allocations per rank. 0 when everything matched
+ * and no more than per_cycle slots were ever in use. */
+int slb_rdv_slot_selftest(const char* id128, int rank, int world, int cycles, int per_cycle);
+/* Page-locked host memory for slb_from_host_async / slb_to_host_async (cudaHostAlloc). NULL on failure. */
+void* slb_pinned_alloc(size_t n);
+void slb_pinned_free(void* p);
 
 #ifdef __cplusplus
 }

@@ -7,7 +7,7 @@
  *
  * Parity status: PINNED. The restatement is checked (tests/test_oracle.py) against torch.optim.AdamW on CPU
  * with the reference's own recipe (tests/test_ops.py:121-134, rtol 1e-5 / atol 1e-6), and on a GPU
- * (tests/test_reference_gpu.py) bit for bit against the reference's own k_adamw (core/cuda/kernels.cu:242-254)
+ * (tests/test_gpu_reference.py) bit for bit against the reference's own k_adamw (core/cuda/kernels.cu:242-254)
  * compiled unmodified into oracle/_ref/. The cross-rank summation order of NCCL (the reference's all-reduce,
  * core/cuda/kernels.cu:773-775) is a third-party detail the reference does not pin; the order used here is the
  * fixed rank order the product guarantees: ((g0 + g1) + g2) + ... then one multiply by 1/world.
@@ -116,6 +116,49 @@ double oracle_clip(float* const* g, const int64_t* n, int ntensors, double max_n
         for (int t = 0; t < ntensors; t++) oracle_scale(g[t], g[t], n[t], s);
     }
     return norm;
+}
+
+
+/*
+ * Sum of squares the way the two-shot gradient mean accumulates it for the clip that follows
+ * (python/soliton/optim.py:31-39 asks for it tensor by tensor; the reference answers with cublasSdot,
+ * core/cuda/kernels.cu:219-224, whose summation order is not pinned). A "piece" is the part of one tensor that one
+ * thread block reduces in one go: tiles [tile_a, tile_b) of the tensor, 2048 floats each, the last one of a tensor
+ * possibly shorter. 256 threads each keep one double: in a whole tile of a 32-byte aligned tensor (vec != 0)
+ * thread t squares elements 8t .. 8t+7 in order, in any other tile elements t, t+256, ...; every square enters with
+ * one fused multiply-add. At the end of the piece the 32 lanes of a warp combine in a halving tree (lane l adds
+ * lane l + 16, then + 8, ...), and the eight warp results are added in warp order.
+ */
+double oracle_sumsq_piece(const float* x, int64_t n, int64_t tile_a, int64_t tile_b, int vec) {
+    enum { TILE = 2048, THREADS = 256 };
+    double acc[THREADS];
+    for (int t = 0; t < THREADS; t++) acc[t] = 0.0;
+    for (int64_t k = tile_a; k < tile_b; k++) {
+        const int64_t base = k * TILE;
+        const int64_t cnt = n - base < TILE ? n - base : TILE;
+        if (vec && cnt == TILE) {
+            for (int t = 0; t < THREADS; t++)
+                for (int j = 0; j < 8; j++) {
+                    const double v = (double)x[base + 8 * t + j];
+                    acc[t] = fma(v, v, acc[t]);
+                }
+        } else {
+            for (int t = 0; t < THREADS; t++)
+                for (int64_t e = t; e < cnt; e += THREADS) {
+                    const double v = (double)x[base + e];
+                    acc[t] = fma(v, v, acc[t]);
+                }
+        }
+    }
+    double total = 0.0;
+    for (int w = 0; w < THREADS / 32; w++) {
+        double lane[32];
+        for (int l = 0; l < 32; l++) lane[l] = acc[32 * w + l];
+        for (int o = 16; o; o >>= 1)
+            for (int l = 0; l < o; l++) lane[l] = lane[l] + lane[l + o];
+        total += lane[0];
+    }
+    return total;
 }
 
 /* ---- timing harness for the CPU baseline: `threads` host ranks each run the whole per-rank path ---- */

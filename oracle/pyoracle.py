@@ -19,6 +19,7 @@ def lib():
         _lib.oracle_sumsq.restype = C.c_double
         _lib.oracle_clip.restype = C.c_double
         _lib.oracle_bench.restype = C.c_double
+        _lib.oracle_sumsq_piece.restype = C.c_double
     return _lib
 
 
@@ -69,3 +70,37 @@ def bench(p0, grads, reps, threads):
     """Seconds for `reps` host steps (sum ranks, scale, adamw) on each of `threads` threads; the slowest thread."""
     arr = (FP * len(grads))(*[_fp(g) for g in grads])
     return lib().oracle_bench(_fp(p0), arr, C.c_int(len(grads)), C.c_int64(p0.size), C.c_int(reps), C.c_int(threads))
+
+
+TILE = 2048
+
+
+def sumsq_pieces(tensors, world, blocks, vec=True):
+    """Per-tensor sum of squares as the two-shot gradient mean leaves it behind: the step's tensors, each padded to
+    whole tiles, form one tile sequence; rank c's chunk is tiles [T*c//world, T*(c+1)//world), block b's run inside a
+    chunk of length L starts at L*b//blocks. A piece starts where a run starts and where a tensor starts; a tensor's
+    pieces are added in tile order. `vec`: per tensor (or one flag for all) whether it is 32-byte aligned."""
+    ns = [int(t.size) for t in tensors]
+    prefix = [0]
+    for n in ns:
+        prefix.append(prefix[-1] + (n + TILE - 1) // TILE)
+    total = prefix[-1]
+    starts = set(prefix[i] for i in range(len(ns)) if prefix[i + 1] > prefix[i])
+    for c in range(world):
+        cb = total * c // world
+        length = total * (c + 1) // world - cb
+        for b in range(blocks):
+            r0, r1 = cb + length * b // blocks, cb + length * (b + 1) // blocks
+            if r1 > r0:
+                starts.add(r0)
+    bounds = sorted(starts) + [total]
+    flags = [vec] * len(ns) if isinstance(vec, bool) else list(vec)
+    sums = [0.0] * len(ns)
+    seg = 0
+    for lo, hi in zip(bounds[:-1], bounds[1:]):
+        while prefix[seg + 1] <= lo:
+            seg += 1
+        x = np.ascontiguousarray(tensors[seg], np.float32).ravel()
+        sums[seg] += lib().oracle_sumsq_piece(_fp(x), C.c_int64(x.size), C.c_int64(lo - prefix[seg]),
+                                              C.c_int64(hi - prefix[seg]), C.c_int(1 if flags[seg] else 0))
+    return sums

@@ -18,6 +18,9 @@ static Engine& E() { return Engine::get(); }
 static inline void before_memory_op(int dev) {
     if (dev == DEV_CUDA) E().flush();  // nothing pending may outlive memory it points into
 }
+static inline void before_release(int dev, const void* p, size_t n) {
+    if (dev == DEV_CUDA && E().cuda_ready()) E().before_release(p, n);  // nor may work in flight on another stream
+}
 
 extern "C" {
 
@@ -27,7 +30,7 @@ void* sl_alloc(int dev, size_t n) { return valid_dev(dev) ? pool(dev).alloc(n) :
 
 void sl_free(int dev, void* p, size_t n) {
     if (!valid_dev(dev)) return;
-    before_memory_op(dev);
+    before_release(dev, p, n);
     pool(dev).release(p, n);
 }
 
@@ -97,8 +100,7 @@ static void copy_any(int dev, void* dst, const void* src, size_t n, cudaMemcpyKi
     if (dev == DEV_CPU) {
         memcpy(dst, src, n);
     } else if (dev == DEV_CUDA) {
-        E().flush();
-        if (cudaMemcpy(dst, src, n, kind) != cudaSuccess) E().set_error(ERR_SYNC);
+        E().copy_blocking(dst, src, n, (int)kind);
     }
 }
 void sl_from_host(int dev, void* dst, const void* src, size_t n) { copy_any(dev, dst, src, n, cudaMemcpyHostToDevice); }
@@ -171,7 +173,12 @@ int slb_set_option(const char* name, int64_t value) {
     if (!strcmp(name, "eager")) o.eager = (int)value;
     else if (!strcmp(name, "mode")) o.mode = (int)value;
     else if (!strcmp(name, "blocks_per_sm")) o.blocks_per_sm = (int)value;
-    else if (!strcmp(name, "pipeline")) o.pipeline = (int)value;
+    else if (!strcmp(name, "prefetch")) o.prefetch = (int)value;
+    else if (!strcmp(name, "stamps")) o.stamps = (int)value;
+    else if (!strcmp(name, "overlap")) {
+        if (E().cuda_ready()) E().sync();  // launches change stream: nothing may be in flight across the switch
+        o.overlap = (int)value;
+    }
     else if (!strcmp(name, "cyclic")) o.cyclic = (int)value;
     else if (!strcmp(name, "timeout_ms")) o.timeout_ns = (unsigned long long)value * 1000000ull;
     else if (!strcmp(name, "host_timeout_ms")) o.host_timeout_s = (double)value / 1000.0;
@@ -187,10 +194,20 @@ int64_t slb_get_counter(const char* name) {
     if (!strcmp(name, "last_blocks")) return E().last_blocks;
     if (!strcmp(name, "world")) return E().world();
     if (!strcmp(name, "sm_count")) return E().sm_count();
+    if (!strcmp(name, "pending_frees")) return E().pending_frees();
     return -1;
 }
 
 void slb_flush(void) { E().flush(); }
+
+int slb_from_host_async(int k, void* const* dst, const void* const* src, const size_t* bytes) {
+    return E().from_host_async(k, dst, src, bytes);
+}
+int slb_to_host_async(int k, void* const* dst, const void* const* src, const size_t* bytes) {
+    return E().to_host_async(k, dst, src, bytes);
+}
+int slb_wait_copies(void) { return E().wait_copies(); }
+int slb_read_stamps(uint64_t* out5) { return E().read_stamps(reinterpret_cast<unsigned long long*>(out5)); }
 void slb_clear_error(void) { E().clear_error(); }
 
 int64_t slb_tile_count(const int64_t* n, int nseg) {
@@ -209,9 +226,10 @@ void slb_run_range(int64_t tiles, int world, int chunk, int blocks, int block, i
 
 int slb_sim_step(int world, int nseg, const int64_t* n, float* const* p, float* const* g, float* const* m,
                  float* const* v, const float* wd, float lr, float b1, float b2, float eps, int step, int adam,
-                 int mode, int blocks_per_rank, int64_t timeout_ms, unsigned active_mask, int* status_out) {
+                 int mode, int blocks_per_rank, int64_t timeout_ms, unsigned active_mask, int* status_out,
+                 double* sumsq_out) {
     return E().sim_step(world, nseg, n, p, g, m, v, wd, lr, b1, b2, eps, step, adam, mode, blocks_per_rank,
-                        (unsigned long long)timeout_ms * 1000000ull, active_mask, status_out);
+                        (unsigned long long)timeout_ms * 1000000ull, active_mask, status_out, sumsq_out);
 }
 
 int slb_rdv_create_id(char* out128) { return Rendezvous::create_id(out128); }
@@ -229,7 +247,7 @@ int slb_rdv_selftest(const char* id128, int rank, int world, int rounds) {
     for (int k = 1; rc == 0 && k <= rounds; k++) {
         const uint32_t nseg = 3 + (k / 2) % 2;
         std::vector<RdvSegment> t(nseg);
-        for (uint32_t s = 0; s < nseg; s++) t[s] = RdvSegment{(uint32_t)rank, 0, (uint64_t)(1000 * rank + 16 * (k / 2) + s), (int64_t)(7 * s + 1)};
+        for (uint32_t s = 0; s < nseg; s++) t[s] = RdvSegment{(uint32_t)rank, 1, (uint64_t)(1000 * rank + 16 * (k / 2) + s), (int64_t)(7 * s + 1)};
         if (r.arrive((uint64_t)k, t.data(), nseg, wait_s) != 0) {
             rc = -3;
             break;
@@ -250,6 +268,76 @@ int slb_rdv_selftest(const char* id128, int rank, int world, int rounds) {
     if (r.stage_barrier(2, wait_s) != 0 && rc == 0) rc = -7;
     r.close();
     return rc;
+}
+
+// Export slot life cycle without CUDA: every cycle each rank publishes `per_cycle` fake allocations, the peers check
+// what they read, the owner asks for them back, the peers acknowledge, the owner recycles the slots. More
+// allocations pass through than the table has slots.
+int slb_rdv_slot_selftest(const char* id128, int rank, int world, int cycles, int per_cycle) {
+    Rendezvous r;
+    const double wait_s = E().opt.host_timeout_s;
+    if (per_cycle < 1 || per_cycle > 256 || r.open(id128, rank, world, wait_s) != 0) return -1;
+    int rc = r.stage_barrier(1, wait_s) != 0 ? -2 : 0;
+    if (rc == 0) r.unlink_now();
+    uint64_t k = 0;
+    std::vector<int> mine((size_t)per_cycle);
+    std::vector<RdvSegment> t((size_t)per_cycle);
+    for (int c = 0; rc == 0 && c < cycles; c++) {
+        for (int i = 0; i < per_cycle; i++) {
+            unsigned char h[64];
+            for (int b = 0; b < 64; b++) h[b] = (unsigned char)(rank * 31 + c * 7 + i * 3 + b);
+            mine[i] = r.add_export(h, (uint64_t)(1000 + c));
+            if (mine[i] < 0) return -3;  // ran out of slots: recycling does not work
+            t[i] = RdvSegment{(uint32_t)mine[i], r.generation_of((uint32_t)mine[i]), (uint64_t)i, 1};
+        }
+        if (r.arrive(++k, t.data(), (uint32_t)per_cycle, wait_s) != 0) rc = -4;
+        for (int q = 0; rc == 0 && q < world; q++) {
+            uint32_t n2 = 0;
+            uint64_t ver = 0;
+            const RdvSegment* pt = r.table_of(q, k, &n2, &ver);
+            for (int i = 0; rc == 0 && i < per_cycle; i++) {
+                const RdvExport& x = r.peer(q).exports[pt[i].export_id];
+                if (x.generation != pt[i].generation || x.size != (uint64_t)(1000 + c) ||
+                    x.handle[5] != (unsigned char)(q * 31 + c * 7 + i * 3 + 5))
+                    rc = -5;
+            }
+        }
+        for (int i = 0; i < per_cycle; i++) r.mark_freed((uint32_t)mine[i]);
+        if (rc == 0 && r.arrive(++k, t.data(), (uint32_t)per_cycle, wait_s) != 0) rc = -6;
+        for (int q = 0; rc == 0 && q < world; q++) {
+            if (q == rank) continue;
+            uint32_t n2 = 0;
+            uint64_t ver = 0;
+            const RdvSegment* pt = r.table_of(q, k, &n2, &ver);
+            for (int i = 0; i < per_cycle; i++) {
+                if (!r.peer(q).exports[pt[i].export_id].freed.load()) rc = -7;
+                r.ack_freed(q, pt[i].export_id);
+            }
+        }
+        if (rc == 0 && r.arrive(++k, t.data(), (uint32_t)per_cycle, wait_s) != 0) rc = -8;
+        for (int i = 0; rc == 0 && i < per_cycle; i++) {
+            if (!r.released_by_all((uint32_t)mine[i])) rc = -9;
+            r.recycle((uint32_t)mine[i]);
+        }
+    }
+    const uint32_t used = r.self().n_exports.load();
+    if (rc == 0 && used > (uint32_t)per_cycle) rc = -10;  // slots were reused, not appended
+    if (rc != 0) r.fail();
+    if (r.stage_barrier(2, wait_s) != 0 && rc == 0) rc = -11;
+    r.close();
+    return rc;
+}
+
+void* slb_pinned_alloc(size_t n) {
+    void* p = nullptr;
+    if (cudaHostAlloc(&p, n ? n : 1, cudaHostAllocPortable) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    return p;
+}
+void slb_pinned_free(void* p) {
+    if (p) cudaFreeHost(p);
 }
 
 }  // extern "C"

@@ -5,21 +5,24 @@
 //
 // The path is bandwidth-bound (28 algorithmic HBM bytes per parameter, no contraction), so the kernels are built
 // around memory traffic: 256-bit coalesced accesses, every thread issuing all loads of a tile before it touches
-// the data (3 + ranks independent 32-byte loads per thread), streaming cache hints for local tensors, one
-// launch for all tensors of a step, and grids sized to the number of blocks that are resident at once.
-// Peer gradients are read and written directly through NVSwitch-mapped pointers; no library collective runs.
+// the data, streaming cache hints for local tensors, one launch for all tensors of a step, and grids sized to the
+// number of blocks that are resident at once. Peer gradients are read and written directly through
+// NVSwitch-mapped pointers; no library collective runs.
 //
-//   k_twoshot<W,ADAM>  reduce-scatter + all-gather. Rank c owns chunk c of the tile sequence: it pulls that chunk
-//                      from every rank, sums in rank order 0..W-1, multiplies by 1/W, stores the mean into its own
-//                      gradient and (ADAM) updates its own p, m, v on the spot. Then it pulls every other chunk's
+//   k_twoshot<W,ADAM,AHEAD>  reduce-scatter + all-gather. Rank c owns chunk c of the tile sequence: it pulls that
+//                      chunk from every rank, sums in rank order 0..W-1, multiplies by 1/W, stores the mean into its
+//                      own gradient and (ADAM) updates its own p, m, v on the spot. Then it pulls every other chunk's
 //                      mean from its owner, stores it into its local gradient and updates p, m, v there.
 //                      With W == 1 this is the plain multi-tensor AdamW step.
+//                      AHEAD: loads that cross NVLink run a few tiles ahead of the arithmetic. A peer load takes
+//                      several microseconds under load, and with one 32-byte load per thread outstanding an SM holds
+//                      16 KiB in flight, which caps the link near 600 GB/s. AHEAD_SMEM stages the peers' tiles in a
+//                      shared-memory ring filled by cp.async (no registers held while in flight, 56 KiB per block);
+//                      AHEAD_REGS keeps a short ring in registers; AHEAD_NONE issues a tile's loads when it needs them.
+//                      Without an optimizer (ADAM = false) the owner also accumulates the sum of squares of the
+//                      mean it produces, piece by piece, for the gradient clip that follows such a launch.
 //   k_oneshot<W,ADAM>  for small steps: every rank pushes its gradients into a staging slot on every peer, one
 //                      barrier, then every rank reduces all W copies locally in the same rank order.
-//   k_step<W,ADAM>     the same exchange as k_twoshot with the tiles staged through a shared-memory ring that the
-//                      bulk-copy engine fills and drains (loader thread / compute warps / storer thread) and with
-//                      the mean published slice by slice. Measured slower than k_twoshot at every world size, so
-//                      it only runs when the "pipeline" option asks for it.
 //
 // All of them produce the same bits: the sum is ((g0 + g1) + g2) + ... in float, then one multiply by 1/W, whoever
 // computes it; so weights stay bit-identical across ranks and across the one-shot/two-shot choice.
@@ -40,7 +43,7 @@
 namespace slb {
 
 enum Mode : int { REDUCE_OWN = 0, GATHER = 1, PUSH = 2, REDUCE_STAGED = 3 };
-enum Barrier : int { B_START = 0, B_REDUCED = 1, B_DONE = 2, B_SLICE = 3 };  // rows of the flag area; B_SLICE + j
+enum Barrier : int { B_START = 0, B_REDUCED = 1, B_DONE = 2 };  // rows of the flag area
 
 // ---------------------------------------------------------------- memory primitives
 
@@ -59,14 +62,6 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
 }
 // Gradient data that another GPU may have written during this launch (or that lives on another GPU): strong
 // system-scope loads, which never hit a stale L1 line. Ordered after the acquiring flag poll by program order.
-__device__ __forceinline__ float4 ld_sys4(const float* p) {
-    float4 v;
-    asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];"
-                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-                 : "l"(p)
-                 : "memory");
-    return v;
-}
 __device__ __forceinline__ float ld_sys1(const float* p) {
     float v;
     asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
@@ -85,6 +80,7 @@ __device__ __forceinline__ float8 ld_sys8(const float* p) {
                  : "memory");
     return v;
 }
+// Local tensors that are read once and written once per step: streaming (evict-first) accesses.
 __device__ __forceinline__ float8 ld_stream8(const float* p) {
     float8 v;
     asm volatile("ld.global.cs.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
@@ -103,9 +99,6 @@ __device__ __forceinline__ void st_plain8(float* p, const float8& v) {
                  "f"(v.lo.w), "f"(v.hi.x), "f"(v.hi.y), "f"(v.hi.z), "f"(v.hi.w)
                  : "memory");
 }
-// Local tensors that are read once and written once per step: streaming (evict-first) accesses.
-__device__ __forceinline__ float4 ld_stream4(const float* p) { return __ldcs(reinterpret_cast<const float4*>(p)); }
-__device__ __forceinline__ void st_stream4(float* p, float4 v) { __stcs(reinterpret_cast<float4*>(p), v); }
 
 // ---------------------------------------------------------------- AdamW arithmetic
 
@@ -114,6 +107,8 @@ __device__ __forceinline__ void st_stream4(float* p, float4 v) { __stcs(reinterp
 // The operands here are floats promoted to double and bias corrections in (0, 1], far from the exponent limits,
 // so the checked range is not needed. Each routine ends in FMA residual corrections that make the result the
 // correctly rounded one (Markstein's construction); the GPU tests compare every bit with IEEE division / sqrt.
+// Infinite operands (a second moment that overflowed float) would turn the Newton steps into NaN; they are passed
+// through by a select at the end of each routine, with the value IEEE arithmetic gives.
 __device__ __forceinline__ double rcp_seed(double d) {
     double y;
     asm("rcp.approx.ftz.f64 %0, %1;" : "=d"(y) : "d"(d));
@@ -124,13 +119,15 @@ __device__ __forceinline__ double rsqrt_seed(double x) {
     asm("rsqrt.approx.ftz.f64 %0, %1;" : "=d"(y) : "d"(x));
     return y;
 }
-// a / b with y = RN(1 / b) supplied (b is a launch constant; the host rounds its reciprocal correctly).
+__device__ __forceinline__ bool is_inf(double x) { return fabs(x) == __longlong_as_double(0x7ff0000000000000LL); }
+// a / b with y = RN(1 / b) supplied (b is a launch constant in (0, 1]; the host rounds its reciprocal correctly).
 __device__ __forceinline__ double div_by_const(double a, double b, double y) {
     double q = __dmul_rn(a, y);
     double r = __fma_rn(-b, q, a);
     q = __fma_rn(r, y, q);      // faithful
     r = __fma_rn(-b, q, a);
-    return __fma_rn(r, y, q);   // correctly rounded
+    q = __fma_rn(r, y, q);      // correctly rounded
+    return is_inf(a) ? a : q;   // inf / b = inf for b > 0
 }
 __device__ __forceinline__ double div_exact(double a, double d) {
     double y = rcp_seed(d);                     // ~20 bits
@@ -140,7 +137,13 @@ __device__ __forceinline__ double div_exact(double a, double d) {
     y = __fma_rn(y, e, y);                      // full precision, within an ulp
     e = __fma_rn(-d, y, 1.0);
     y = __fma_rn(y, e, y);                      // RN(1 / d)
-    return div_by_const(a, d, y);
+    double q = __dmul_rn(a, y);
+    double r = __fma_rn(-d, q, a);
+    q = __fma_rn(r, y, q);
+    r = __fma_rn(-d, q, a);
+    q = __fma_rn(r, y, q);
+    // d = +inf (d is a square root plus eps, never negative): finite / inf = signed zero, inf / inf = NaN
+    return is_inf(d) ? __dmul_rn(a, 0.0) : (is_inf(a) ? a : q);
 }
 __device__ __forceinline__ double sqrt_exact(double x) {
     const double y = rsqrt_seed(x);             // ~20 bits of 1 / sqrt(x)
@@ -153,7 +156,7 @@ __device__ __forceinline__ double sqrt_exact(double x) {
     g = __fma_rn(rem, h, g);
     rem = __fma_rn(-g, g, x);
     g = __fma_rn(rem, h, g);
-    return x == 0.0 ? 0.0 : g;                  // the seed of 0 is inf; sqrt(0) is 0
+    return (x == 0.0 || is_inf(x)) ? x : g;     // the seed of 0 is inf and the seed of inf is 0; sqrt returns both as is
 }
 
 // One element of the reference update (core/cuda/kernels.cu:242-250) with every rounding written out, so that the
@@ -180,16 +183,44 @@ __device__ __forceinline__ float4 add4(const float4& a, const float4& b) {
 __device__ __forceinline__ float4 mul4(const float4& a, float s) {
     return make_float4(__fmul_rn(a.x, s), __fmul_rn(a.y, s), __fmul_rn(a.z, s), __fmul_rn(a.w, s));
 }
+__device__ __forceinline__ float8 add8(const float8& a, const float8& b) {
+    float8 r;
+    r.lo = add4(a.lo, b.lo), r.hi = add4(a.hi, b.hi);
+    return r;
+}
+__device__ __forceinline__ float8 mul8(const float8& a, float s) {
+    float8 r;
+    r.lo = mul4(a.lo, s), r.hi = mul4(a.hi, s);
+    return r;
+}
+__device__ __forceinline__ float8 sel8(bool c, const float8& a, const float8& b) {
+    float8 r;
+    r.lo = make_float4(c ? a.lo.x : b.lo.x, c ? a.lo.y : b.lo.y, c ? a.lo.z : b.lo.z, c ? a.lo.w : b.lo.w);
+    r.hi = make_float4(c ? a.hi.x : b.hi.x, c ? a.hi.y : b.hi.y, c ? a.hi.z : b.hi.z, c ? a.hi.w : b.hi.w);
+    return r;
+}
+// acc += x^2 over the eight floats of v, in element order, in double (one FMA each).
+__device__ __forceinline__ double sumsq8(double acc, const float8& v) {
+    acc = __fma_rn((double)v.lo.x, (double)v.lo.x, acc);
+    acc = __fma_rn((double)v.lo.y, (double)v.lo.y, acc);
+    acc = __fma_rn((double)v.lo.z, (double)v.lo.z, acc);
+    acc = __fma_rn((double)v.lo.w, (double)v.lo.w, acc);
+    acc = __fma_rn((double)v.hi.x, (double)v.hi.x, acc);
+    acc = __fma_rn((double)v.hi.y, (double)v.hi.y, acc);
+    acc = __fma_rn((double)v.hi.z, (double)v.hi.z, acc);
+    acc = __fma_rn((double)v.hi.w, (double)v.hi.w, acc);
+    return acc;
+}
 
 // ---------------------------------------------------------------- segment lookup
 
-// The segment a block is currently inside, held in registers; refilled only when a tile leaves its range.
-template <int W>
+// The segment a block is currently inside, held in registers; refilled only when a tile leaves its range. The
+// peers' gradient pointers stay in the table: one warp-uniform, cached 8-byte load whenever one is needed.
 struct SegView {
     float *p, *m, *v;
-    float* g[W];   // REDUCE_OWN: every rank's gradient
     float* gme;    // this rank's gradient
     float* gsrc;   // GATHER: the owner's gradient
+    const Seg* sg;
     int64_t n;
     float wd, gscale;
     int hyper, vec;
@@ -209,26 +240,31 @@ __device__ __forceinline__ int find_seg(const int* prefix, int nseg, int t) {
     return lo;
 }
 
-template <int W>
-__device__ __forceinline__ void load_seg(SegView<W>& s, const RankCtx& c, const int* prefix, int t, int me, int src) {
+// Rank r's gradient of a segment, as mapped on this rank. The table does not change while a kernel runs.
+__device__ __forceinline__ float* peer_grad(const Seg* sg, int r) {
+    return reinterpret_cast<float*>(__ldg(reinterpret_cast<const unsigned long long*>(&sg->g[r])));
+}
+
+__device__ __forceinline__ void load_seg(SegView& s, const RankCtx& c, const int* prefix, int t, int me, int src) {
     const int i = find_seg(prefix, c.nseg, t);
     const Seg* sg = c.segs + i;
+    s.sg = sg;
     s.p = sg->p, s.m = sg->m, s.v = sg->v;
-#pragma unroll
-    for (int r = 0; r < W; r++) s.g[r] = sg->g[r];
-    s.gme = sg->g[me];
-    s.gsrc = sg->g[src];
+    s.gme = peer_grad(sg, me);
+    s.gsrc = peer_grad(sg, src);
     s.n = sg->n, s.wd = sg->wd, s.gscale = sg->gscale, s.hyper = sg->hyper, s.vec = sg->vec;
     s.first_tile = prefix[i], s.end_tile = prefix[i + 1];
 }
 
-// ---------------------------------------------------------------- one tile
+// ---------------------------------------------------------------- one tile, every load issued up front
 
 // Processes tile t of the sequence in the given mode. `stage` (one-shot only) is the base of the staging half in
-// use on this rank; peers' halves come from c.stage[r] + stage_off.
+// use on this rank; peers' halves come from c.stage[r] + stage_off. `ssq` collects the squares of the mean this
+// tile produces (REDUCE_OWN of several ranks without an optimizer); untouched otherwise.
 template <int W, bool ADAM, int MODE>
-__device__ __forceinline__ void do_tile(const SegView<W>& s, const LaunchArgs& a, const RankCtx& c, int t, int me,
-                                        const float* stage, size_t stage_off) {
+__device__ __forceinline__ void do_tile(const SegView& s, const LaunchArgs& a, const RankCtx& c, int t, int me,
+                                        const float* stage, size_t stage_off, double& ssq) {
+    constexpr bool SUMSQ = W > 1 && !ADAM && MODE == REDUCE_OWN;
     const int tid = threadIdx.x;
     const int64_t base = (int64_t)(t - s.first_tile) * kTile;
     const int64_t left = s.n - base;
@@ -247,7 +283,7 @@ __device__ __forceinline__ void do_tile(const SegView<W>& s, const LaunchArgs& a
                 gv[0] = ld_stream8(s.gme + off);
             } else {
 #pragma unroll
-                for (int r = 0; r < W; r++) gv[r] = ld_sys8(s.g[r] + off);
+                for (int r = 0; r < W; r++) gv[r] = ld_sys8(peer_grad(s.sg, r) + off);
             }
         } else if (MODE == GATHER) {
             gv[0] = ld_sys8(s.gsrc + off);
@@ -271,14 +307,15 @@ __device__ __forceinline__ void do_tile(const SegView<W>& s, const LaunchArgs& a
             float8 avg = gv[0];
             if (MODE != GATHER && W > 1) {
 #pragma unroll
-                for (int r = 1; r < W; r++) avg.lo = add4(avg.lo, gv[r].lo), avg.hi = add4(avg.hi, gv[r].hi);
-                avg.lo = mul4(avg.lo, a.inv_world), avg.hi = mul4(avg.hi, a.inv_world);
+                for (int r = 1; r < W; r++) avg = add8(avg, gv[r]);
+                avg = mul8(avg, a.inv_world);
             }
             if (W == 1 && s.gscale != 1.0f) {  // clipped gradient: y = alpha * x in float, kept in place
-                avg.lo = mul4(avg.lo, s.gscale), avg.hi = mul4(avg.hi, s.gscale);
+                avg = mul8(avg, s.gscale);
                 st_stream8(s.gme + off, avg);
             }
             if (W > 1) st_stream8(s.gme + off, avg);
+            if (SUMSQ) ssq = sumsq8(ssq, avg);
             if (adam) {
                 adamw_vec(pv.lo, avg.lo, mv.lo, vv.lo, h, s.wd);
                 adamw_vec(pv.hi, avg.hi, mv.hi, vv.hi, h, s.wd);
@@ -308,7 +345,7 @@ __device__ __forceinline__ void do_tile(const SegView<W>& s, const LaunchArgs& a
 #pragma unroll
                 for (int r = 0; r < W; r++) {
                     if (MODE == REDUCE_OWN)
-                        x[r] = ld_sys1(s.g[r] + off);
+                        x[r] = ld_sys1(peer_grad(s.sg, r) + off);
                     else
                         x[r] = r == me ? ld_sys1(s.gme + off) : ld_sys1(stage + (size_t)r * slot + (size_t)t * kTile + e);
                 }
@@ -322,6 +359,7 @@ __device__ __forceinline__ void do_tile(const SegView<W>& s, const LaunchArgs& a
                 s.gme[off] = avg;
             }
             if (W > 1) s.gme[off] = avg;
+            if (SUMSQ) ssq = __fma_rn((double)avg, (double)avg, ssq);
             if (adam) {
                 float p = s.p[off], m = s.m[off], v = s.v[off];
                 adamw_elem(p, avg, m, v, h, s.wd);
@@ -331,15 +369,393 @@ __device__ __forceinline__ void do_tile(const SegView<W>& s, const LaunchArgs& a
     }
 }
 
+// A contiguous run of tiles in one mode, tile by tile (single-rank steps and both halves of one-shot).
 template <int W, bool ADAM, int MODE>
 __device__ __forceinline__ void do_run(const LaunchArgs& a, const RankCtx& c, const int* prefix, int t0, int t1, int me,
                                        int src, const float* stage, size_t stage_off) {
-    SegView<W> s;
+    SegView s;
     s.first_tile = 0, s.end_tile = 0;
+    double unused = 0;
     for (int t = t0; t < t1; t++) {
-        if (t >= s.end_tile || t < s.first_tile) load_seg<W>(s, c, prefix, t, me, src);
-        do_tile<W, ADAM, MODE>(s, a, c, t, me, stage, stage_off);
+        if (t >= s.end_tile || t < s.first_tile) load_seg(s, c, prefix, t, me, src);
+        do_tile<W, ADAM, MODE>(s, a, c, t, me, stage, stage_off, unused);
     }
+}
+
+// ---------------------------------------------------------------- the two halves of two-shot, peer loads running ahead
+
+// AHEAD_REGS. How many tiles the peer loads of the reduce half run ahead of the arithmetic, held in a register ring:
+// W - 1 peer streams per tile. 0: all W loads of a tile are issued together and nothing runs ahead (from four ranks
+// on a single tile already has three or more peer loads per thread outstanding).
+template <int W, bool ADAM>
+constexpr int kReduceAhead = W == 2 ? 2 : (W == 3 ? 1 : 0);
+// Tiles the single peer stream of the gather half runs ahead. More than these, and the optimizer variants spill.
+template <bool ADAM>
+constexpr int kGatherAhead = ADAM ? 2 : 4;
+
+// Where the loads that run ahead currently are: the segment of the tile they fetch.
+struct Ahead {
+    const Seg* sg;
+    float* gsrc;
+    int64_t n;
+    int vec, first, end;
+};
+__device__ __forceinline__ bool ahead_seek(Ahead& ah, const RankCtx& c, const int* prefix, int t, int src) {
+    if (t >= ah.end || t < ah.first) {
+        const int i = find_seg(prefix, c.nseg, t);
+        ah.sg = c.segs + i;
+        ah.gsrc = peer_grad(ah.sg, src);
+        ah.n = ah.sg->n, ah.vec = ah.sg->vec, ah.first = prefix[i], ah.end = prefix[i + 1];
+    }
+    return ah.vec && ah.n - (int64_t)(t - ah.first) * kTile >= kTile;  // a whole, aligned tile: the 256-bit path
+}
+
+// The sum of squares of the mean a block produced since `first`: per thread in element order, then a fixed tree.
+struct Piece {
+    double acc;
+    int first;
+};
+// Closes the open piece: the block's sum goes to entry `first` of every rank's partial table (the staging area,
+// which two-shot launches do not use otherwise). The host adds a tensor's pieces in tile order. All threads call.
+template <int W>
+__device__ __forceinline__ void flush_piece(const RankCtx& c, Piece& pc, double* s_red) {
+    double acc = pc.acc;
+    for (int o = 16; o; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
+    __syncthreads();  // the previous piece's s_red has been read
+    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double t = 0;
+        for (int w = 0; w < kThreads / 32; w++) t += s_red[w];
+        s_red[kThreads / 32] = t;
+    }
+    __syncthreads();
+    // thread r tells rank r; the same thread later posts the flag that publishes this store to that rank
+    if (threadIdx.x < W) reinterpret_cast<double*>(c.stage[threadIdx.x])[pc.first] = s_red[kThreads / 32];
+    pc.acc = 0;
+}
+
+// Value of rank R in the rank-ordered sum: this rank's own gradient at position `me`, the peers' (held without the
+// own one, in rank order) around it. `me` is not a compile-time constant, hence the selects.
+template <int W, int R>
+__device__ __forceinline__ float8 rank_value(int me, const float8& own, const float8 (&peer)[W - 1]) {
+    if constexpr (R == 0)
+        return sel8(me == 0, own, peer[0]);
+    else if constexpr (R == W - 1)
+        return sel8(me == W - 1, own, peer[W - 2]);
+    else
+        return sel8(R == me, own, sel8(R < me, peer[R], peer[R - 1]));
+}
+// ((x0 + x1) + x2) + ... + xR
+template <int W, int R>
+struct RankSum {
+    static __device__ __forceinline__ float8 upto(int me, const float8& own, const float8 (&peer)[W - 1]) {
+        return add8(RankSum<W, R - 1>::upto(me, own, peer), rank_value<W, R>(me, own, peer));
+    }
+};
+template <int W>
+struct RankSum<W, 0> {
+    static __device__ __forceinline__ float8 upto(int me, const float8& own, const float8 (&peer)[W - 1]) {
+        return rank_value<W, 0>(me, own, peer);
+    }
+};
+
+template <int W>
+__device__ __forceinline__ void ahead_reduce(Ahead& ah, float8 (&slot)[W - 1], const RankCtx& c, const int* prefix, int t,
+                                             int t1, int me, int e) {
+    if (t >= t1) return;
+    if (!ahead_seek(ah, c, prefix, t, me)) return;
+    const int64_t off = (int64_t)(t - ah.first) * kTile + e;
+#pragma unroll
+    for (int k = 0; k < W - 1; k++) slot[k] = ld_sys8(peer_grad(ah.sg, k + (k >= me ? 1 : 0)) + off);
+}
+
+// Reduce half: the run [t0, t1) of this rank's own chunk. Mean in rank order, stored into the own gradient, and
+// the update of the own p, m, v (ADAM) or the sum of squares of the mean (no optimizer) on the spot.
+template <int W, bool ADAM, int AHEAD>
+__device__ __forceinline__ void reduce_run(const LaunchArgs& a, const RankCtx& c, const int* prefix, int t0, int t1, int me,
+                                           double* s_red) {
+    constexpr int D = AHEAD == AHEAD_REGS ? kReduceAhead<W, ADAM> : 0;
+    constexpr int RD = D > 0 ? D : 1;
+    constexpr bool SUMSQ = !ADAM;
+    const bool pieces = SUMSQ && a.sumsq_on;
+    float8 ring[RD][W - 1];  // D > 0: the peers' values of tiles t .. t + D - 1
+    SegView s;
+    s.first_tile = 0, s.end_tile = 0;
+    Ahead ah;
+    ah.first = 0, ah.end = 0;
+    Piece pc;
+    pc.acc = 0, pc.first = t0;
+    const int e = threadIdx.x * 8;
+    if (D > 0) {
+#pragma unroll
+        for (int j = 0; j < RD; j++) ahead_reduce<W>(ah, ring[j], c, prefix, t0 + j, t1, me, e);
+    }
+    for (int tb = t0; tb < t1; tb += RD) {
+#pragma unroll
+        for (int j = 0; j < RD; j++) {
+            const int t = tb + j;
+            if (t >= t1) break;
+            if (t >= s.end_tile || t < s.first_tile) {
+                if (pieces && t > pc.first) flush_piece<W>(c, pc, s_red);
+                load_seg(s, c, prefix, t, me, me);
+                pc.first = t;
+            }
+            const int64_t base = (int64_t)(t - s.first_tile) * kTile;
+            if (D > 0 && s.vec && s.n - base >= kTile) {
+                const int64_t off = base + e;
+                const bool adam = ADAM && s.p != nullptr;
+                const float8 own = ld_sys8(s.gme + off);
+                float8 pv, mv, vv;
+                if (adam) {
+                    pv = ld_stream8(s.p + off);
+                    mv = ld_stream8(s.m + off);
+                    vv = ld_stream8(s.v + off);
+                }
+                float8 peer[W - 1];
+#pragma unroll
+                for (int k = 0; k < W - 1; k++) peer[k] = ring[j][k];
+                ahead_reduce<W>(ah, ring[j], c, prefix, t + D, t1, me, e);  // the slot is free: fetch tile t + D into it
+                const float8 avg = mul8(RankSum<W, W - 1>::upto(me, own, peer), a.inv_world);
+                st_stream8(s.gme + off, avg);
+                if (SUMSQ) pc.acc = sumsq8(pc.acc, avg);
+                if (adam) {
+                    const Hyper& h = a.hp[s.hyper];
+                    adamw_vec(pv.lo, avg.lo, mv.lo, vv.lo, h, s.wd);
+                    adamw_vec(pv.hi, avg.hi, mv.hi, vv.hi, h, s.wd);
+                    st_stream8(s.p + off, pv);
+                    st_stream8(s.m + off, mv);
+                    st_stream8(s.v + off, vv);
+                }
+            } else {
+                if (D > 0) ahead_reduce<W>(ah, ring[j], c, prefix, t + D, t1, me, e);
+                do_tile<W, ADAM, REDUCE_OWN>(s, a, c, t, me, nullptr, 0, pc.acc);
+            }
+        }
+    }
+    if (pieces && t1 > pc.first) flush_piece<W>(c, pc, s_red);
+}
+
+__device__ __forceinline__ void ahead_gather(Ahead& ah, float8& slot, const RankCtx& c, const int* prefix, int t, int t1,
+                                             int src, int e) {
+    if (t >= t1) return;
+    if (!ahead_seek(ah, c, prefix, t, src)) return;
+    slot = ld_sys8(ah.gsrc + (int64_t)(t - ah.first) * kTile + e);
+}
+
+// Gather half: the run [t0, t1) of chunk `src`, whose mean its owner has published. Copies the mean into the local
+// gradient and updates the local p, m, v with it.
+template <int W, bool ADAM, int AHEAD>
+__device__ __forceinline__ void gather_run(const LaunchArgs& a, const RankCtx& c, const int* prefix, int t0, int t1, int me,
+                                           int src) {
+    constexpr int D = AHEAD == AHEAD_REGS ? kGatherAhead<ADAM> : 0;
+    constexpr int RD = D > 0 ? D : 1;
+    float8 ring[RD];  // D > 0: the owner's values of tiles t .. t + D - 1
+    SegView s;
+    s.first_tile = 0, s.end_tile = 0;
+    Ahead ah;
+    ah.first = 0, ah.end = 0;
+    double unused = 0;
+    const int e = threadIdx.x * 8;
+    if (D > 0) {
+#pragma unroll
+        for (int j = 0; j < RD; j++) ahead_gather(ah, ring[j], c, prefix, t0 + j, t1, src, e);
+    }
+    for (int tb = t0; tb < t1; tb += RD) {
+#pragma unroll
+        for (int j = 0; j < RD; j++) {
+            const int t = tb + j;
+            if (t >= t1) break;
+            if (t >= s.end_tile || t < s.first_tile) load_seg(s, c, prefix, t, me, src);
+            const int64_t base = (int64_t)(t - s.first_tile) * kTile;
+            if (D > 0 && s.vec && s.n - base >= kTile) {
+                const int64_t off = base + e;
+                const bool adam = ADAM && s.p != nullptr;
+                float8 pv, mv, vv;
+                if (adam) {
+                    pv = ld_stream8(s.p + off);
+                    mv = ld_stream8(s.m + off);
+                    vv = ld_stream8(s.v + off);
+                }
+                const float8 avg = ring[j];
+                ahead_gather(ah, ring[j], c, prefix, t + D, t1, src, e);  // the slot is free: fetch tile t + D into it
+                st_stream8(s.gme + off, avg);
+                if (adam) {
+                    const Hyper& h = a.hp[s.hyper];
+                    adamw_vec(pv.lo, avg.lo, mv.lo, vv.lo, h, s.wd);
+                    adamw_vec(pv.hi, avg.hi, mv.hi, vv.hi, h, s.wd);
+                    st_stream8(s.p + off, pv);
+                    st_stream8(s.m + off, mv);
+                    st_stream8(s.v + off, vv);
+                }
+            } else {
+                if (D > 0) ahead_gather(ah, ring[j], c, prefix, t + D, t1, src, e);
+                do_tile<W, ADAM, GATHER>(s, a, c, t, me, nullptr, 0, unused);
+            }
+        }
+    }
+}
+
+
+// ---------------------------------------------------------------- the two halves of two-shot, peer tiles staged in shared memory
+
+// AHEAD_SMEM. The peer loads of both halves go through a ring of tile-sized stages in shared memory, filled by
+// asynchronous copies (cp.async, 16 bytes each, L2-only so no stale L1 line can serve them) that cost no registers
+// while they are in flight: kRingStages tiles of one peer stream in the gather half, kRingStages / (W - 1) tiles of
+// all W - 1 peer streams in the reduce half. A thread copies, waits for and reads back only its own 32 bytes of
+// each stage, so the ring needs no block-wide synchronisation. Ragged tiles and unaligned tensors bypass the ring.
+__device__ __forceinline__ void cp_async16(float* smem_dst, const float* gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(smem_dst)), "l"(gsrc)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {  // all but the N most recent groups of this thread have landed
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ float8 ld_smem8(const float* p) {
+    float8 v;
+    v.lo = reinterpret_cast<const float4*>(p)[0];
+    v.hi = reinterpret_cast<const float4*>(p)[1];
+    return v;
+}
+template <int W>
+constexpr int kStagedReduceAhead = kRingStages / (W - 1) > 0 ? kRingStages / (W - 1) : 1;
+// From six ranks on the reduce half keeps its loads in registers, all W of a tile at once: that already is five or
+// more peer loads per thread in flight, and holding W - 1 staged tiles next to p, m, v would spill.
+constexpr int kStagedReduceMaxWorld = 5;
+
+// Starts the copies of tile t of the reduce half into stage `slot` (W - 1 peer streams) and closes the group;
+// the group is empty when t lies beyond the run or is not a whole aligned tile, so that groups stay one per tile.
+template <int W>
+__device__ __forceinline__ void stage_reduce(Ahead& ah, float* slot, const RankCtx& c, const int* prefix, int t, int t1,
+                                             int me, int e) {
+    if (t < t1 && ahead_seek(ah, c, prefix, t, me)) {
+        const int64_t off = (int64_t)(t - ah.first) * kTile + e;
+#pragma unroll
+        for (int k = 0; k < W - 1; k++) {
+            const float* g = peer_grad(ah.sg, k + (k >= me ? 1 : 0)) + off;
+            cp_async16(slot + k * kTile + e, g);
+            cp_async16(slot + k * kTile + e + 4, g + 4);
+        }
+    }
+    cp_async_commit();
+}
+
+template <int W, bool ADAM>
+__device__ __forceinline__ void reduce_run_staged(const LaunchArgs& a, const RankCtx& c, const int* prefix, float* ring,
+                                                  int t0, int t1, int me, double* s_red) {
+    constexpr int D = kStagedReduceAhead<W>;
+    constexpr int kStage = (W - 1) * kTile;  // floats per stage
+    constexpr bool SUMSQ = !ADAM;
+    const bool pieces = SUMSQ && a.sumsq_on;
+    SegView s;
+    s.first_tile = 0, s.end_tile = 0;
+    Ahead ah;
+    ah.first = 0, ah.end = 0;
+    Piece pc;
+    pc.acc = 0, pc.first = t0;
+    const int e = threadIdx.x * 8;
+    for (int j = 0; j < D; j++) stage_reduce<W>(ah, ring + j * kStage, c, prefix, t0 + j, t1, me, e);
+    int j = 0;
+    for (int t = t0; t < t1; t++) {
+        float* slot = ring + j * kStage;
+        j = j + 1 == D ? 0 : j + 1;
+        if (t >= s.end_tile || t < s.first_tile) {
+            if (pieces && t > pc.first) flush_piece<W>(c, pc, s_red);
+            load_seg(s, c, prefix, t, me, me);
+            pc.first = t;
+        }
+        const int64_t base = (int64_t)(t - s.first_tile) * kTile;
+        if (s.vec && s.n - base >= kTile) {
+            const int64_t off = base + e;
+            const bool adam = ADAM && s.p != nullptr;
+            const float8 own = ld_sys8(s.gme + off);
+            float8 pv, mv, vv;
+            if (adam) {
+                pv = ld_stream8(s.p + off);
+                mv = ld_stream8(s.m + off);
+                vv = ld_stream8(s.v + off);
+            }
+            cp_async_wait<D - 1>();  // tile t's group is the oldest of the D outstanding
+            float8 peer[W - 1];
+#pragma unroll
+            for (int k = 0; k < W - 1; k++) peer[k] = ld_smem8(slot + k * kTile + e);
+            stage_reduce<W>(ah, slot, c, prefix, t + D, t1, me, e);  // the stage is free: tile t + D goes into it
+            const float8 avg = mul8(RankSum<W, W - 1>::upto(me, own, peer), a.inv_world);
+            st_stream8(s.gme + off, avg);
+            if (SUMSQ) pc.acc = sumsq8(pc.acc, avg);
+            if (adam) {
+                const Hyper& h = a.hp[s.hyper];
+                adamw_vec(pv.lo, avg.lo, mv.lo, vv.lo, h, s.wd);
+                adamw_vec(pv.hi, avg.hi, mv.hi, vv.hi, h, s.wd);
+                st_stream8(s.p + off, pv);
+                st_stream8(s.m + off, mv);
+                st_stream8(s.v + off, vv);
+            }
+        } else {
+            stage_reduce<W>(ah, slot, c, prefix, t + D, t1, me, e);
+            do_tile<W, ADAM, REDUCE_OWN>(s, a, c, t, me, nullptr, 0, pc.acc);
+        }
+    }
+    cp_async_wait<0>();
+    if (pieces && t1 > pc.first) flush_piece<W>(c, pc, s_red);
+}
+
+__device__ __forceinline__ void stage_gather(Ahead& ah, float* slot, const RankCtx& c, const int* prefix, int t, int t1,
+                                             int src, int e) {
+    if (t < t1 && ahead_seek(ah, c, prefix, t, src)) {
+        const float* g = ah.gsrc + (int64_t)(t - ah.first) * kTile + e;
+        cp_async16(slot + e, g);
+        cp_async16(slot + e + 4, g + 4);
+    }
+    cp_async_commit();
+}
+
+template <int W, bool ADAM>
+__device__ __forceinline__ void gather_run_staged(const LaunchArgs& a, const RankCtx& c, const int* prefix, float* ring,
+                                                  int t0, int t1, int me, int src) {
+    constexpr int D = kRingStages;
+    SegView s;
+    s.first_tile = 0, s.end_tile = 0;
+    Ahead ah;
+    ah.first = 0, ah.end = 0;
+    double unused = 0;
+    const int e = threadIdx.x * 8;
+    for (int j = 0; j < D; j++) stage_gather(ah, ring + j * kTile, c, prefix, t0 + j, t1, src, e);
+    int j = 0;
+    for (int t = t0; t < t1; t++) {
+        float* slot = ring + j * kTile;
+        j = j + 1 == D ? 0 : j + 1;
+        if (t >= s.end_tile || t < s.first_tile) load_seg(s, c, prefix, t, me, src);
+        const int64_t base = (int64_t)(t - s.first_tile) * kTile;
+        if (s.vec && s.n - base >= kTile) {
+            const int64_t off = base + e;
+            const bool adam = ADAM && s.p != nullptr;
+            float8 pv, mv, vv;
+            if (adam) {
+                pv = ld_stream8(s.p + off);
+                mv = ld_stream8(s.m + off);
+                vv = ld_stream8(s.v + off);
+            }
+            cp_async_wait<D - 1>();
+            const float8 avg = ld_smem8(slot + e);
+            stage_gather(ah, slot, c, prefix, t + D, t1, src, e);
+            st_stream8(s.gme + off, avg);
+            if (adam) {
+                const Hyper& h = a.hp[s.hyper];
+                adamw_vec(pv.lo, avg.lo, mv.lo, vv.lo, h, s.wd);
+                adamw_vec(pv.hi, avg.hi, mv.hi, vv.hi, h, s.wd);
+                st_stream8(s.p + off, pv);
+                st_stream8(s.m + off, mv);
+                st_stream8(s.v + off, vv);
+            }
+        } else {
+            stage_gather(ah, slot, c, prefix, t + D, t1, src, e);
+            do_tile<W, ADAM, GATHER>(s, a, c, t, me, nullptr, 0, unused);
+        }
+    }
+    cp_async_wait<0>();
 }
 
 // ---------------------------------------------------------------- flag barriers
@@ -381,14 +797,26 @@ __device__ __forceinline__ void await(const RankCtx& c, const LaunchArgs& a, int
 
 __device__ __forceinline__ int cut(int total, int part, int parts) { return (int)((int64_t)total * part / parts); }
 
+// Device time of block 0 at the borders of a launch's phases (start, peers present, own chunk reduced, all chunks
+// gathered, peers done), for the host to read afterwards. Off when the rank context carries no stamp area.
+__device__ __forceinline__ void stamp(const RankCtx& c, int block, int i) {
+    if (c.stamps != nullptr && block == 0 && threadIdx.x == 0) c.stamps[i] = global_ns();
+}
+
 // ---------------------------------------------------------------- kernels
+
+// The ring of stages behind the tile prefix in dynamic shared memory.
+__device__ __forceinline__ float* ring_of(int* s_prefix, int nseg) {
+    return reinterpret_cast<float*>(reinterpret_cast<char*>(s_prefix) + prefix_smem_bytes(nseg));
+}
 
 // Resident blocks per SM the single-rank kernel is compiled for (80 registers per thread).
 constexpr int kLocalBlocksPerSm = 3;
-template <int W, bool ADAM>
+template <int W, bool ADAM, int AHEAD>
 __global__ void __launch_bounds__(kThreads, W == 1 ? kLocalBlocksPerSm : 2) k_twoshot(const __grid_constant__ LaunchArgs a) {
-    extern __shared__ int s_prefix[];
+    extern __shared__ __align__(128) int s_prefix[];  // tile prefix, then (AHEAD_SMEM) the ring of stages
     __shared__ int s_abort;
+    __shared__ double s_red[kThreads / 32 + 1];
     const int G = a.blocks_per_rank;
     const int b = blockIdx.x % G;
     const RankCtx& c = a.ctxs[blockIdx.x / G];
@@ -398,40 +826,58 @@ __global__ void __launch_bounds__(kThreads, W == 1 ? kLocalBlocksPerSm : 2) k_tw
     __syncthreads();
     const int T = s_prefix[nseg];
 
-    if (W > 1) {
+    if constexpr (W == 1) {
+        if (a.cyclic > 0) {
+            // block-cyclic order: block b takes groups b, b + G, ... of `cyclic` consecutive tiles, so that the
+            // resident blocks walk through each tensor stream side by side instead of in G far-apart places
+            const int C = a.cyclic, groups = (T + C - 1) / C;
+            SegView s;
+            s.first_tile = 0, s.end_tile = 0;
+            double unused = 0;
+            for (int j = b; j < groups; j += G) {
+                const int t1 = (j + 1) * C < T ? (j + 1) * C : T;
+                for (int t = j * C; t < t1; t++) {
+                    if (t >= s.end_tile || t < s.first_tile) load_seg(s, c, s_prefix, t, me, me);
+                    do_tile<W, ADAM, REDUCE_OWN>(s, a, c, t, me, nullptr, 0, unused);
+                }
+            }
+        } else {
+            do_run<W, ADAM, REDUCE_OWN>(a, c, s_prefix, cut(T, b, G), cut(T, b + 1, G), me, me, nullptr, 0);
+        }
+    } else {
+        stamp(c, b, 0);
         post<W>(c, B_START, b, me, a.seq);
         await<W>(c, a, B_START, b, me, -1, ST_TIMEOUT_START, &s_abort);
-    }
-    if (W == 1 && a.cyclic > 0) {
-        // single rank, block-cyclic order: block b takes groups b, b + G, ... of `cyclic` consecutive tiles, so that
-        // the resident blocks walk through each tensor stream side by side instead of in G far-apart places
-        const int C = a.cyclic, groups = (T + C - 1) / C;
-        SegView<W> s;
-        s.first_tile = 0, s.end_tile = 0;
-        for (int j = b; j < groups; j += G) {
-            const int t1 = (j + 1) * C < T ? (j + 1) * C : T;
-            for (int t = j * C; t < t1; t++) {
-                if (t >= s.end_tile || t < s.first_tile) load_seg<W>(s, c, s_prefix, t, me, me);
-                do_tile<W, ADAM, REDUCE_OWN>(s, a, c, t, me, nullptr, 0);
+        stamp(c, b, 1);
+        {   // own chunk: reduce, scale, update
+            const int cb = cut(T, me, W), ce = cut(T, me + 1, W), L = ce - cb;
+            const int r0 = cb + cut(L, b, G), r1 = cb + cut(L, b + 1, G);
+            if (s_abort) {
+            } else if constexpr (AHEAD == AHEAD_SMEM && W <= kStagedReduceMaxWorld) {
+                reduce_run_staged<W, ADAM>(a, c, s_prefix, ring_of(s_prefix, nseg), r0, r1, me, s_red);
+            } else {
+                reduce_run<W, ADAM, AHEAD>(a, c, s_prefix, r0, r1, me, s_red);
             }
         }
-        return;
-    }
-    {   // own chunk: reduce, scale, update
-        const int cb = cut(T, me, W), ce = cut(T, me + 1, W), L = ce - cb;
-        if (!s_abort) do_run<W, ADAM, REDUCE_OWN>(a, c, s_prefix, cb + cut(L, b, G), cb + cut(L, b + 1, G), me, me, nullptr, 0);
-    }
-    if (W > 1) {
+        stamp(c, b, 2);
         post<W>(c, B_REDUCED, b, me, a.seq);
         for (int k = 1; k < W; k++) {  // other chunks, starting after the own one so that owners are hit evenly
             const int src = (me + k) % W;
             await<W>(c, a, B_REDUCED, b, me, src, ST_TIMEOUT_REDUCED, &s_abort);
             const int cb = cut(T, src, W), ce = cut(T, src + 1, W), L = ce - cb;
-            if (!s_abort) do_run<W, ADAM, GATHER>(a, c, s_prefix, cb + cut(L, b, G), cb + cut(L, b + 1, G), me, src, nullptr, 0);
+            const int r0 = cb + cut(L, b, G), r1 = cb + cut(L, b + 1, G);
+            if (s_abort) {
+            } else if constexpr (AHEAD == AHEAD_SMEM) {
+                gather_run_staged<W, ADAM>(a, c, s_prefix, ring_of(s_prefix, nseg), r0, r1, me, src);
+            } else {
+                gather_run<W, ADAM, AHEAD>(a, c, s_prefix, r0, r1, me, src);
+            }
         }
+        stamp(c, b, 3);
         // nobody may reuse or free gradient memory that a peer is still reading
         post<W>(c, B_DONE, b, me, a.seq);
         await<W>(c, a, B_DONE, b, me, -1, ST_TIMEOUT_DONE, &s_abort);
+        stamp(c, b, 4);
     }
 }
 
@@ -455,410 +901,6 @@ __global__ void __launch_bounds__(kThreads, 2) k_oneshot(const __grid_constant__
     post<W>(c, B_REDUCED, b, me, a.seq);
     await<W>(c, a, B_REDUCED, b, me, -1, ST_TIMEOUT_REDUCED, &s_abort);
     if (!s_abort) do_run<W, ADAM, REDUCE_STAGED>(a, c, s_prefix, t0, t1, me, me, c.stage[me] + stage_off, stage_off);
-}
-
-// ---------------------------------------------------------------- shared-memory pipeline (bulk async copies)
-
-// k_step streams its tiles through a ring of shared-memory stages filled and drained by the bulk-copy engine
-// (cp.async.bulk, the untiled TMA path), so that the bytes in flight per SM are set by the ring depth and not by
-// how many loads the compute warps happen to have outstanding; that is what keeps NVLink pulls (microseconds of
-// latency) and HBM streams saturated while the warps do double-precision arithmetic. Three roles per block:
-//   warp 8, lane 0  loader:   waits for a free stage, issues one 4 KiB bulk load per input stream into it
-//   warps 0-7       compute:  wait for the stage's bytes, reduce / update in place in shared memory
-//   warp 9, lane 0  storer:   issues one bulk store per output stream (remote gradients included), frees stages
-// A pipeline step covers kSub floats of every stream (one float4 per compute thread); a tile is two steps.
-// Only whole, 16-byte aligned tiles go through the ring; ragged ends and unaligned tensors take do_tile().
-constexpr int kSub = 4 * kThreads;
-constexpr int kSubBytes = kSub * 4;
-constexpr int kSubsPerTile = kTile / kSub;
-constexpr int kMaxStages = 8;
-constexpr int kPipeThreads = kThreads + 64;
-constexpr int kPipeHeader = 256;  // mbarriers and the abort word, ahead of the tile prefix and the stages
-
-struct Pipe {
-    uint64_t *full, *computed, *empty;  // kMaxStages mbarriers each
-    int* abort;
-    unsigned char* data;
-    int stages, stage_bytes;
-};
-
-__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint64_t* b, unsigned count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(b)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* b) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(b)) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect(uint64_t* b, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(b)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint64_t* b, unsigned parity) {
-    unsigned ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(smem_addr(b)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded: gives up when another role of the block already did, or after LaunchArgs::timeout_ns.
-__device__ __forceinline__ bool mbar_wait(uint64_t* b, unsigned parity, const LaunchArgs& a, const RankCtx& c,
-                                          volatile int* abort) {
-    if (mbar_try(b, parity)) return true;
-    const unsigned long long t0 = global_ns();
-    unsigned spins = 0;
-    while (!mbar_try(b, parity)) {
-        if ((++spins & 63) == 0) {
-            if (*abort) return false;
-            if (global_ns() - t0 > a.timeout_ns) {
-                atomicCAS(c.status, 0, ST_TIMEOUT_PIPE);
-                *abort = 1;
-                return false;
-            }
-        }
-    }
-    return true;
-}
-__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, unsigned bytes, uint64_t* bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                     smem_addr(smem_dst)),
-                 "l"(gsrc), "r"(bytes), "r"(smem_addr(bar))
-                 : "memory");
-}
-__device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, unsigned bytes) {
-    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_addr(smem_src)),
-                 "r"(bytes)
-                 : "memory");
-}
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void bulk_wait_read() {
-    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
-}
-__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-__device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async;" ::: "memory"); }
-__device__ __forceinline__ void fence_async_proxy_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-
-// What the three roles share while they walk the same list of work items. An item is a range of tiles in one
-// mode: REDUCE_OWN (pull the tiles from every rank, mean in rank order, store it into the own gradient, update own
-// p/m/v) or GATHER (pull the finished mean from its owner `src`, store it into the local gradient, update p/m/v;
-// src == me, the single-rank step, reads the local gradient and stores no gradient).
-// A ring step of REDUCE_OWN covers one sub-tile (kSub floats) of W gradient streams plus p, m, v. A step of GATHER
-// has only four streams, so it covers as many sub-tiles as fit the same stage (`gsubs`, 1 or 2).
-template <int W>
-struct Walk {
-    const LaunchArgs& a;
-    const RankCtx& c;
-    const Pipe& pp;
-    const int* prefix;
-    int me, block, src;
-    unsigned it;      // ring steps so far: stage index and mbarrier parity; equal in all roles at item borders
-    SegView<W> s;
-    __device__ Walk(const LaunchArgs& a_, const RankCtx& c_, const Pipe& pp_, const int* prefix_, int me_, int block_)
-        : a(a_), c(c_), pp(pp_), prefix(prefix_), me(me_), block(block_), src(me_), it(0) {
-        s.first_tile = 0, s.end_tile = 0;
-    }
-    __device__ __forceinline__ volatile int* abort() const { return pp.abort; }
-    __device__ __forceinline__ void set_src(int src_) {
-        if (src_ != src) s.first_tile = 0, s.end_tile = 0;  // the view caches the owner's pointer
-        src = src_;
-    }
-    // Positions the segment view on tile t; true when the tile goes through the ring.
-    template <bool ADAM>
-    __device__ __forceinline__ bool ring_tile(int t, int64_t* base, bool* adam) {
-        if (t >= s.end_tile || t < s.first_tile) load_seg<W>(s, c, prefix, t, me, src);
-        *base = (int64_t)(t - s.first_tile) * kTile;
-        *adam = ADAM && s.p != nullptr;
-        return s.vec && s.n - *base >= kTile;
-    }
-};
-
-// Slots one gathered sub-tile takes in a stage (gradient, and p, m, v with an optimizer), and how many sub-tiles a
-// GATHER step covers: as many as fit the stage, which is sized for a REDUCE_OWN step of W + 3 (or W) slots.
-template <bool ADAM>
-constexpr int kGatherSlots = ADAM ? 4 : 1;
-template <int W, bool ADAM>
-constexpr int kGatherSubs =
-    ((W > 1 ? W : 1) + (ADAM ? 3 : 0)) / kGatherSlots<ADAM> >= kSubsPerTile ? kSubsPerTile : 1;
-
-// Tiles of [t0, t1) that cannot take the ring (ragged ends, unaligned tensors): plain accesses by the compute warps.
-template <int W, bool ADAM, int MODE>
-__device__ __forceinline__ void ragged_pass(Walk<W>& w, int t0, int t1, int src) {
-    if (threadIdx.x >= kThreads) return;
-    w.set_src(src);
-    for (int t = t0; t < t1; t++) {
-        int64_t base;
-        bool adam;
-        if (w.template ring_tile<ADAM>(t, &base, &adam)) continue;
-        do_tile<W, ADAM, MODE>(w.s, w.a, w.c, t, w.me, nullptr, 0);
-    }
-}
-
-// ---- loader: one thread. wait_row >= 0: the tiles are written by rank `src` during this launch; wait (bounded)
-// for its flag first.
-template <int W, bool ADAM, int MODE>
-__device__ __forceinline__ void load_item(Walk<W>& w, int t0, int t1, int wait_row) {
-    constexpr int GS = kGatherSubs<W, ADAM>, SL = kGatherSlots<ADAM>;
-    const Pipe& pp = w.pp;
-    if (*w.abort()) return;
-    if (wait_row >= 0) {
-        const unsigned* f = w.c.flags[w.me] + flag_index(wait_row, w.block, w.src);
-        const unsigned long long start = global_ns();
-        while ((int)(ld_acquire_sys(f) - w.a.seq) < 0) {
-            if (global_ns() - start > w.a.timeout_ns) {
-                atomicCAS(w.c.status, 0, ST_TIMEOUT_REDUCED);
-                *w.abort() = 1;
-                return;
-            }
-            __nanosleep(32);
-        }
-    }
-    fence_async_proxy();  // what generic-proxy flags made visible is read by the bulk-copy engine from here on
-    for (int t = t0; t < t1; t++) {
-        if (*w.abort()) return;
-        int64_t base;
-        bool adam;
-        if (!w.template ring_tile<ADAM>(t, &base, &adam)) continue;
-        const int per = MODE == REDUCE_OWN ? 1 : GS;
-        for (int sub = 0; sub < kSubsPerTile; sub += per, w.it++) {
-            const int stage = w.it % pp.stages;
-            if (!mbar_wait(pp.empty + stage, ((w.it / pp.stages) & 1) ^ 1, w.a, w.c, w.abort())) return;
-            unsigned char* dst = pp.data + (size_t)stage * pp.stage_bytes;
-            uint64_t* bar = pp.full + stage;
-            if (MODE == REDUCE_OWN) {
-                const int64_t off = base + sub * kSub;
-                mbar_arrive_expect(bar, (unsigned)((W + (adam ? 3 : 0)) * kSubBytes));
-#pragma unroll
-                for (int r = 0; r < W; r++) bulk_load(dst + r * kSubBytes, w.s.g[r] + off, kSubBytes, bar);
-                if (adam) {
-                    bulk_load(dst + W * kSubBytes, w.s.p + off, kSubBytes, bar);
-                    bulk_load(dst + (W + 1) * kSubBytes, w.s.m + off, kSubBytes, bar);
-                    bulk_load(dst + (W + 2) * kSubBytes, w.s.v + off, kSubBytes, bar);
-                }
-            } else {
-                mbar_arrive_expect(bar, (unsigned)(per * (1 + (adam ? 3 : 0)) * kSubBytes));
-#pragma unroll
-                for (int q = 0; q < per; q++) {
-                    const int64_t off = base + (sub + q) * kSub;
-                    unsigned char* d = dst + q * SL * kSubBytes;
-                    bulk_load(d, w.s.gsrc + off, kSubBytes, bar);  // crosses NVLink unless src == me
-                    if (adam) {
-                        bulk_load(d + kSubBytes, w.s.p + off, kSubBytes, bar);
-                        bulk_load(d + 2 * kSubBytes, w.s.m + off, kSubBytes, bar);
-                        bulk_load(d + 3 * kSubBytes, w.s.v + off, kSubBytes, bar);
-                    }
-                }
-            }
-        }
-    }
-}
-
-// ---- compute warps: 256 threads, one float4 of every stream and sub-tile each, in place in shared memory.
-template <int W, bool ADAM, int MODE>
-__device__ __forceinline__ void compute_item(Walk<W>& w, int t0, int t1) {
-    constexpr int GS = kGatherSubs<W, ADAM>, SL = kGatherSlots<ADAM>;
-    const Pipe& pp = w.pp;
-    for (int t = t0; t < t1; t++) {
-        if (*w.abort()) return;
-        int64_t base;
-        bool adam;
-        if (!w.template ring_tile<ADAM>(t, &base, &adam)) continue;
-        const Hyper& h = w.a.hp[w.s.hyper];
-        const int per = MODE == REDUCE_OWN ? 1 : GS;
-        for (int sub = 0; sub < kSubsPerTile; sub += per, w.it++) {
-            const int stage = w.it % pp.stages;
-            if (!mbar_wait(pp.full + stage, (w.it / pp.stages) & 1, w.a, w.c, w.abort())) return;
-            float4* st = reinterpret_cast<float4*>(pp.data + (size_t)stage * pp.stage_bytes) + threadIdx.x;
-            if (MODE == REDUCE_OWN) {
-                float4 avg = st[0];
-#pragma unroll
-                for (int r = 1; r < W; r++) avg = add4(avg, st[r * kThreads]);
-                if (W > 1) {
-                    avg = mul4(avg, w.a.inv_world);
-                    st[0] = avg;
-                }
-                if (adam) {
-                    float4 p = st[W * kThreads], m = st[(W + 1) * kThreads], v = st[(W + 2) * kThreads];
-                    adamw_vec(p, avg, m, v, h, w.s.wd);
-                    st[W * kThreads] = p, st[(W + 1) * kThreads] = m, st[(W + 2) * kThreads] = v;
-                }
-            } else if (adam) {
-#pragma unroll
-                for (int q = 0; q < per; q++) {
-                    float4* sq = st + q * SL * kThreads;
-                    float4 avg = sq[0];
-                    if (W == 1 && w.s.gscale != 1.0f) {
-                        avg = mul4(avg, w.s.gscale);
-                        sq[0] = avg;
-                    }
-                    float4 p = sq[kThreads], m = sq[2 * kThreads], v = sq[3 * kThreads];
-                    adamw_vec(p, avg, m, v, h, w.s.wd);
-                    sq[kThreads] = p, sq[2 * kThreads] = m, sq[3 * kThreads] = v;
-                }
-            }
-            fence_async_proxy_smem();  // the bulk stores read what was just written through the generic proxy
-            mbar_arrive(pp.computed + stage);
-        }
-    }
-}
-
-// ---- storer: one thread. post_row >= 0: once every store of the item has landed, publish the flag to all peers.
-template <int W, bool ADAM, int MODE>
-__device__ __forceinline__ void store_item(Walk<W>& w, int t0, int t1, int post_row) {
-    constexpr int GS = kGatherSubs<W, ADAM>, SL = kGatherSlots<ADAM>;
-    const Pipe& pp = w.pp;
-    for (int t = t0; t < t1; t++) {
-        if (*w.abort()) break;
-        int64_t base;
-        bool adam;
-        if (!w.template ring_tile<ADAM>(t, &base, &adam)) continue;
-        const int per = MODE == REDUCE_OWN ? 1 : GS;
-        for (int sub = 0; sub < kSubsPerTile; sub += per, w.it++) {
-            const int stage = w.it % pp.stages;
-            if (!mbar_wait(pp.computed + stage, (w.it / pp.stages) & 1, w.a, w.c, w.abort())) break;
-            const unsigned char* src = pp.data + (size_t)stage * pp.stage_bytes;
-            if (MODE == REDUCE_OWN) {
-                const int64_t off = base + sub * kSub;
-                if (W > 1) bulk_store(w.s.gme + off, src, kSubBytes);  // the mean: peers pull it from here
-                if (adam) {
-                    bulk_store(w.s.p + off, src + W * kSubBytes, kSubBytes);
-                    bulk_store(w.s.m + off, src + (W + 1) * kSubBytes, kSubBytes);
-                    bulk_store(w.s.v + off, src + (W + 2) * kSubBytes, kSubBytes);
-                }
-            } else {
-#pragma unroll
-                for (int q = 0; q < per; q++) {
-                    const int64_t off = base + (sub + q) * kSub;
-                    const unsigned char* sq = src + q * SL * kSubBytes;
-                    if (w.src != w.me || (W == 1 && w.s.gscale != 1.0f))
-                        bulk_store(w.s.gme + off, sq, kSubBytes);  // the local gradient holds the mean (or the clipped value) too
-                    if (adam) {
-                        bulk_store(w.s.p + off, sq + kSubBytes, kSubBytes);
-                        bulk_store(w.s.m + off, sq + 2 * kSubBytes, kSubBytes);
-                        bulk_store(w.s.v + off, sq + 3 * kSubBytes, kSubBytes);
-                    }
-                }
-            }
-            bulk_commit();
-            bulk_wait_read<0>();  // the stores have read the stage: it can be refilled
-            mbar_arrive(pp.empty + stage);
-        }
-    }
-    if (post_row >= 0) {
-        bulk_wait_all();  // every byte of the item has landed
-        fence_async_proxy();
-        __threadfence_system();
-#pragma unroll
-        for (int r = 0; r < W; r++)
-            if (r != w.me) st_release_sys(w.c.flags[r] + flag_index(post_row, w.block, w.me), w.a.seq);
-    }
-}
-
-// One item, whichever role the calling thread has. src: the rank whose gradient memory a GATHER item reads.
-template <int W, bool ADAM, int MODE>
-__device__ __forceinline__ void run_item(Walk<W>& w, int role, int t0, int t1, int src, int wait_row, int post_row) {
-    if (role > 2) return;
-    w.set_src(src);
-    if (role == 0)
-        compute_item<W, ADAM, MODE>(w, t0, t1);
-    else if (role == 1)
-        load_item<W, ADAM, MODE>(w, t0, t1, wait_row);
-    else
-        store_item<W, ADAM, MODE>(w, t0, t1, post_row);
-}
-
-template <int W, bool ADAM>
-__global__ void __launch_bounds__(kPipeThreads, 2) k_step(const __grid_constant__ LaunchArgs a) {
-    extern __shared__ __align__(128) unsigned char smem[];
-    const int G = a.blocks_per_rank;
-    const int b = blockIdx.x % G;
-    const RankCtx& c = a.ctxs[blockIdx.x / G];
-    const int me = c.rank, nseg = c.nseg;
-    Pipe pp;
-    pp.full = reinterpret_cast<uint64_t*>(smem);
-    pp.computed = pp.full + kMaxStages;
-    pp.empty = pp.full + 2 * kMaxStages;
-    pp.abort = reinterpret_cast<int*>(smem + 3 * kMaxStages * 8);
-    int* s_prefix = reinterpret_cast<int*>(smem + kPipeHeader);
-    pp.data = smem + kPipeHeader + ((((size_t)nseg + 1) * 4 + 127) & ~(size_t)127);
-    pp.stages = a.stages;
-    pp.stage_bytes = ((W > 1 ? W : 1) + (ADAM ? 3 : 0)) * kSubBytes;
-    for (int i = threadIdx.x; i <= nseg; i += kPipeThreads) s_prefix[i] = c.tile_prefix[i];
-    if (threadIdx.x == 0) {
-        for (int i = 0; i < kMaxStages; i++) {
-            mbar_init(pp.full + i, 1);
-            mbar_init(pp.computed + i, kThreads);
-            mbar_init(pp.empty + i, 1);
-        }
-        *pp.abort = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    __syncthreads();
-    const int T = s_prefix[nseg];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // 0: compute (warps 0-7), 1: loader (warp 8, lane 0), 2: storer (warp 9, lane 0), 3: idle lanes of warps 8-9
-    const int role = warp < kThreads / 32 ? 0 : (lane != 0 ? 3 : (warp == kThreads / 32 ? 1 : 2));
-    Walk<W> w(a, c, pp, s_prefix, me, b);
-
-    if (W == 1) {
-        const int t0 = cut(T, b, G), t1 = cut(T, b + 1, G);
-        ragged_pass<W, ADAM, REDUCE_OWN>(w, t0, t1, me);
-        run_item<W, ADAM, GATHER>(w, role, t0, t1, me, -1, -1);
-        if (role == 2) bulk_wait_all();
-        return;
-    }
-
-    // The run of block b inside chunk ch.
-    auto run_of = [&](int ch, int* r0, int* r1) {
-        const int cb = cut(T, ch, W), L = cut(T, ch + 1, W) - cb;
-        *r0 = cb + cut(L, b, G), *r1 = cb + cut(L, b + 1, G);
-    };
-    int own0, own1;
-    run_of(me, &own0, &own1);
-
-    post<W>(c, B_START, b, me, a.seq);
-    await<W>(c, a, B_START, b, me, -1, ST_TIMEOUT_START, pp.abort);
-    // ragged tiles of the own chunk first, published through the block-wide barrier row
-    if (!*pp.abort) ragged_pass<W, ADAM, REDUCE_OWN>(w, own0, own1, me);
-    post<W>(c, B_REDUCED, b, me, a.seq);
-
-    // Whole tiles: the own chunk slice by slice, each slice's mean published as soon as its stores have landed;
-    // one slice behind, the same slice of every other chunk is pulled from its owner. No block ever waits for a
-    // whole phase of a peer, only for the slice it is about to read, which the peer finished a slice ago.
-    for (int j = 0; j <= kSlices; j++) {
-        if (j < kSlices) {
-            const int len = own1 - own0;
-            run_item<W, ADAM, REDUCE_OWN>(w, role, own0 + cut(len, j, kSlices), own0 + cut(len, j + 1, kSlices), me, -1,
-                                          B_SLICE + j);
-        }
-        if (j >= 1) {
-            for (int k = 1; k < W; k++) {
-                const int src = (me + k) % W;
-                int r0, r1;
-                run_of(src, &r0, &r1);
-                const int len = r1 - r0;
-                run_item<W, ADAM, GATHER>(w, role, r0 + cut(len, j - 1, kSlices), r0 + cut(len, j, kSlices), src,
-                                          B_SLICE + j - 1, -1);
-            }
-        }
-    }
-    if (role == 2) {
-        bulk_wait_all();
-        fence_async_proxy();
-    }
-    __syncwarp();
-    await<W>(c, a, B_REDUCED, b, me, -1, ST_TIMEOUT_REDUCED, pp.abort);  // the peers' ragged tiles are reduced
-    if (!*pp.abort) {
-        for (int k = 1; k < W; k++) {
-            const int src = (me + k) % W;
-            int r0, r1;
-            run_of(src, &r0, &r1);
-            ragged_pass<W, ADAM, GATHER>(w, r0, r1, src);
-        }
-    }
-    // nobody may reuse or free gradient memory that a peer is still reading
-    post<W>(c, B_DONE, b, me, a.seq);
-    await<W>(c, a, B_DONE, b, me, -1, ST_TIMEOUT_DONE, pp.abort);
 }
 
 // ---------------------------------------------------------------- small elementwise kernels next to the path
@@ -926,39 +968,42 @@ __global__ void __launch_bounds__(kThreads) k_sumsq_slices(int nslices, const Su
 // ---------------------------------------------------------------- launch
 
 template <int W, bool ADAM>
-static void (*kernel_of(int kind))(const LaunchArgs) {
-    return kind == KERNEL_ONESHOT ? k_oneshot<W, ADAM> : kind == KERNEL_PLAIN ? k_twoshot<W, ADAM> : k_step<W, ADAM>;
+static void (*kernel_of(int kind, int ahead))(const LaunchArgs) {
+    if (kind == KERNEL_ONESHOT) return k_oneshot<W, ADAM>;
+    if (W > 1 && ahead == AHEAD_REGS) return k_twoshot<W, ADAM, (W > 1 ? AHEAD_REGS : AHEAD_NONE)>;
+    if (W > 1 && ahead == AHEAD_SMEM) return k_twoshot<W, ADAM, (W > 1 ? AHEAD_SMEM : AHEAD_NONE)>;
+    return k_twoshot<W, ADAM, AHEAD_NONE>;
+}
+
+// More than 48 KiB of dynamic shared memory has to be allowed per kernel, once.
+static bool allow_smem(const void* kern, size_t smem) {
+    if (smem <= 48 * 1024) return true;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxStepSmem) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return true;
 }
 
 template <int W, bool ADAM>
-static cudaError_t launch_w(int kind, bool cooperative, int grid, size_t smem, const LaunchArgs& a, cudaStream_t st) {
-    void (*kern)(const LaunchArgs) = kernel_of<W, ADAM>(kind);
-    const int threads = kind == KERNEL_STEP ? kPipeThreads : kThreads;
-    if (kind == KERNEL_STEP) {
-        static bool raised = false;  // per instantiation: allow more than 48 KiB of dynamic shared memory
-        if (!raised) {
-            const cudaError_t e = cudaFuncSetAttribute((const void*)kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kStepSmemMax);
-            if (e != cudaSuccess) return e;
-            raised = true;
-        }
-    }
+static cudaError_t launch_w(int kind, int ahead, bool cooperative, int grid, size_t smem, const LaunchArgs& a,
+                            cudaStream_t st) {
+    void (*kern)(const LaunchArgs) = kernel_of<W, ADAM>(kind, ahead);
+    if (!allow_smem((const void*)kern, smem)) return cudaErrorInvalidValue;
     if (cooperative) {
         void* params[] = {const_cast<LaunchArgs*>(&a)};
-        return cudaLaunchCooperativeKernel((const void*)kern, dim3(grid), dim3(threads), params, smem, st);
+        return cudaLaunchCooperativeKernel((const void*)kern, dim3(grid), dim3(kThreads), params, smem, st);
     }
-    kern<<<grid, threads, smem, st>>>(a);
+    kern<<<grid, kThreads, smem, st>>>(a);
     return cudaPeekAtLastError();
 }
 
 template <int W, bool ADAM>
-static int occupancy_w(int kind, size_t smem) {
+static int occupancy_w(int kind, int ahead, size_t smem) {
     int n = 0;
-    void (*kern)(const LaunchArgs) = kernel_of<W, ADAM>(kind);
-    if (kind == KERNEL_STEP &&
-        cudaFuncSetAttribute((const void*)kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kStepSmemMax) != cudaSuccess)
-        return 0;
-    const int threads = kind == KERNEL_STEP ? kPipeThreads : kThreads;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, (const void*)kern, threads, smem) != cudaSuccess) return 0;
+    void (*kern)(const LaunchArgs) = kernel_of<W, ADAM>(kind, ahead);
+    if (!allow_smem((const void*)kern, smem)) return 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, (const void*)kern, kThreads, smem) != cudaSuccess) return 0;
     return n;
 }
 
@@ -974,27 +1019,21 @@ static int occupancy_w(int kind, size_t smem) {
         case 8: return adam ? fn<8, true>(__VA_ARGS__) : fn<8, false>(__VA_ARGS__); \
     }
 
-int launch_step(int world, bool adam, int kind, bool cooperative, int grid, size_t smem, const LaunchArgs& a,
+int launch_step(int world, bool adam, int kind, int ahead, bool cooperative, int grid, size_t smem, const LaunchArgs& a,
                 cudaStream_t st) {
-    SLB_DISPATCH(world, launch_w, kind, cooperative, grid, smem, a, st)
+    SLB_DISPATCH(world, launch_w, kind, ahead, cooperative, grid, smem, a, st)
     return (int)cudaErrorInvalidValue;
 }
 
-int step_occupancy(int world, bool adam, int kind, size_t smem) {
-    SLB_DISPATCH(world, occupancy_w, kind, smem)
+int step_occupancy(int world, bool adam, int kind, int ahead, size_t smem) {
+    SLB_DISPATCH(world, occupancy_w, kind, ahead, smem)
     return 0;
 }
 
-// Shared memory of k_step for a step of nseg segments: header, tile prefix, `stages` stages of one 4 KiB slot per
-// stream. Picks the deepest ring that keeps two blocks resident per SM. Returns 0 when even two stages do not fit.
-size_t step_smem(int world, bool adam, int nseg, int* stages) {
-    const size_t fixed = kPipeHeader + ((((size_t)nseg + 1) * 4 + 127) & ~(size_t)127);
-    const size_t stage = (size_t)((world > 1 ? world : 1) + (adam ? 3 : 0)) * kSubBytes;
-    int n = (int)((kStepSmemMax - fixed) / stage);
-    if (n > kMaxStages) n = kMaxStages;
-    if (n < 2) return 0;
-    *stages = n;
-    return fixed + n * stage;
+size_t step_smem(int world, int kind, int ahead, int nseg) {
+    const size_t prefix = prefix_smem_bytes(nseg);
+    if (world > 1 && kind == KERNEL_PLAIN && ahead == AHEAD_SMEM) return prefix + kRingBytes;
+    return prefix;
 }
 
 static int flat_grid(int64_t n) {
@@ -1088,6 +1127,9 @@ extern "C" int slb_adamw_step_static(int nseg, float* const* p, const float* con
     using namespace slb;
     if (nseg < 1 || !p || !g || !m || !v || !n || step < 1) return -1;
     if (nseg > kStaticMaxSegs) return -2;
+    // Work the engine has recorded but not launched yet (a gradient mean, an in-place clip scale, batched sl_adamw
+    // calls) comes first in stream order, as it came first in call order. Launches planned work only: no allocation.
+    engine_flush_pending();
     unsigned char* dev = static_scratch_address();
     if (!dev) return -3;
 
@@ -1115,7 +1157,7 @@ extern "C" int slb_adamw_step_static(int nseg, float* const* p, const float* con
     ctx->segs = reinterpret_cast<const Seg*>(dev + kStaticSegOff);
     ctx->tile_prefix = reinterpret_cast<const int*>(dev + kStaticPrefixOff);
     ctx->nseg = nseg, ctx->rank = 0, ctx->world = 1;
-    ctx->flags[0] = nullptr, ctx->stage[0] = nullptr;
+    ctx->flags[0] = nullptr, ctx->stage[0] = nullptr, ctx->stamps = nullptr;
     ctx->status = reinterpret_cast<int*>(dev + kStaticStatusOff);
     const size_t used = kStaticSegOff + (size_t)nseg * sizeof(Seg);
     if (cudaMemcpyAsync(dev, image, used, cudaMemcpyHostToDevice, 0) != cudaSuccess) {
@@ -1127,8 +1169,8 @@ extern "C" int slb_adamw_step_static(int nseg, float* const* p, const float* con
     if (cudaGetDevice(&device) != cudaSuccess ||
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
         return -3;
-    const size_t smem = (size_t)(nseg + 1) * sizeof(int);
-    const int per_sm = step_occupancy(1, true, KERNEL_PLAIN, smem);
+    const size_t smem = step_smem(1, KERNEL_PLAIN, AHEAD_NONE, nseg);
+    const int per_sm = step_occupancy(1, true, KERNEL_PLAIN, AHEAD_NONE, smem);
     if (per_sm < 1 || sms < 1) return -3;
     const int64_t cap = (int64_t)per_sm * sms;
     LaunchArgs a{};
@@ -1139,6 +1181,9 @@ extern "C" int slb_adamw_step_static(int nseg, float* const* p, const float* con
     h.bc1 = 1.0 - pow((double)b1, (double)step), h.bc2 = 1.0 - pow((double)b2, (double)step);
     h.rbc1 = 1.0 / h.bc1, h.rbc2 = 1.0 / h.bc2;
     h.lr = lr, h.b1 = b1, h.b2 = b2, h.eps = eps, h.c1 = 1 - b1, h.c2 = 1 - b2;
-    return launch_step(1, true, KERNEL_PLAIN, false, a.blocks_per_rank, smem, a, 0) == 0 ? 0 : -3;
+    a.cyclic = 0;
+    if (launch_step(1, true, KERNEL_PLAIN, AHEAD_NONE, false, a.blocks_per_rank, smem, a, 0) != 0) return -3;
+    engine_count_launch();
+    return 0;
 }
 

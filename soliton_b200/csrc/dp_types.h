@@ -17,8 +17,7 @@ constexpr int kTile = 8 * kThreads; // floats per tile: 2048 (8 KiB per tensor s
 constexpr int kMaxSegs = 4096;      // segments per step
 constexpr int kMaxHyper = 8;        // distinct hyperparameter sets per step
 constexpr int kFlagBlocks = 1024;   // upper bound on blocks per rank that take part in flag barriers
-constexpr int kSlices = 8;          // pieces a block's run of a chunk is cut into; the mean is published per piece
-constexpr int kFlagRows = 3 + kSlices;  // start, reduced, done, then one row per slice
+constexpr int kFlagRows = 3;        // start, reduced, done
 
 // Workspace the path reserves once per device from the deterministic allocator (identically on meta):
 // [control: rank contexts, flag words, segment table, tile prefix][one-shot staging].
@@ -27,11 +26,13 @@ constexpr size_t kStageBytes = size_t(16) << 20;
 constexpr size_t kWorkspaceBytes = kCtlBytes + kStageBytes;  // 18 MiB
 // Offsets inside the control area.
 constexpr size_t kCtxOff = 0;                                   // kMaxWorld rank contexts (emulation uses all)
+constexpr size_t kStampOff = 4096;                              // kStamps device timestamps of the last collective launch
+constexpr int kStamps = 5;                                      // start, peers present, own chunk reduced, gathered, peers done
 constexpr size_t kFlagOff = 8192;                               // kFlagRows x kFlagBlocks x kMaxWorld x 4 B
 constexpr size_t kFlagBytes = size_t(kFlagRows) * kFlagBlocks * kMaxWorld * 4;
-constexpr size_t kTilePrefixOff = kFlagOff + kFlagBytes;        // (kMaxSegs + 1) ints
-constexpr size_t kSegOff = kTilePrefixOff + 32768;              // kMaxSegs segments
-constexpr size_t kPartialOff = kSegOff + size_t(kMaxSegs) * 112;  // kSumsqBlocks doubles (sum-of-squares partials)
+constexpr size_t kTableOff = kFlagOff + kFlagBytes;              // resident step tables: rank context, tile prefix, segments
+constexpr size_t kTableBytes = size_t(768) << 10;                // holds at least one table of kMaxSegs segments
+constexpr size_t kPartialOff = kTableOff + kTableBytes;          // kSumsqBlocks doubles (sum-of-squares partials)
 constexpr int kSumsqBlocks = 1024;
 // Batched sum of squares over many tensors: tensors are cut into slices of kSumsqSlice floats, one partial each.
 constexpr int kSumsqSlice = 65536;
@@ -39,6 +40,8 @@ constexpr int kMaxSumsqSlices = 16384;
 constexpr size_t kSliceTableOff = kPartialOff + size_t(kSumsqBlocks) * 8;          // kMaxSumsqSlices x {ptr, n}
 constexpr size_t kSlicePartialOff = kSliceTableOff + size_t(kMaxSumsqSlices) * 16;  // kMaxSumsqSlices doubles
 static_assert(kSlicePartialOff + size_t(kMaxSumsqSlices) * 8 <= kCtlBytes, "control area layout");
+static_assert(kStampOff + kStamps * 8 <= kFlagOff, "control area layout");
+constexpr int64_t kMaxPieceTiles = (int64_t)(kStageBytes / 8);  // sum-of-squares pieces live in the staging area, by tile
 
 struct SumsqSlice {      // one slice of one tensor
     const float* x;
@@ -76,16 +79,18 @@ struct alignas(16) RankCtx {
     int world;
     int pad;
     unsigned* flags[kMaxWorld];     // flag area of every rank as addressable from this rank; flags[rank] is local
-    float* stage[kMaxWorld];        // one-shot staging area of every rank, likewise
+    float* stage[kMaxWorld];        // one-shot staging area of every rank, likewise; two-shot launches without an
+                                    // optimizer use it as the table of sum-of-squares pieces (doubles, by first tile)
     int* status;                    // first error of this rank's kernels (0 = none); host-mapped
+    unsigned long long* stamps;     // kStamps device times of block 0, or null
 };
+static_assert(sizeof(RankCtx) == 176, "rank context layout");
 
 enum Status : int {
     ST_OK = 0,
     ST_TIMEOUT_START = 21,   // a peer never announced its gradients
     ST_TIMEOUT_REDUCED = 22, // a peer never announced its reduced chunk / its staged gradients
     ST_TIMEOUT_DONE = 23,    // a peer never announced that it finished reading
-    ST_TIMEOUT_PIPE = 24,    // a bulk copy of this block's own shared-memory pipeline never completed
 };
 
 struct LaunchArgs {
@@ -96,7 +101,7 @@ struct LaunchArgs {
     int stage_slot_floats;          // capacity of one (parity, source rank) staging slot
     unsigned long long timeout_ns;  // bound of every flag wait
     float inv_world;
-    int stages;                     // shared-memory pipeline depth of k_step (2..8)
+    int sumsq_on;                   // two-shot without an optimizer: write the sum-of-squares pieces of the mean
     int cyclic;                     // single-rank k_twoshot: > 0 = block-cyclic tile order in groups of this many tiles
     Hyper hp[kMaxHyper];
 };

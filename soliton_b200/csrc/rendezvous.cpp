@@ -76,7 +76,7 @@ int Rendezvous::open(const char id[kIdBytes], int rank, int world, double timeou
     ::close(fd);
     if (m == MAP_FAILED) return -1;
     shm_ = static_cast<RdvShared*>(m);
-    rank_ = rank, world_ = world, owner_ = rank == 0, my_version_ = 0;
+    rank_ = rank, world_ = world, owner_ = rank == 0, my_version_ = 0, n_free_slots_ = 0;
     if (rank == 0) {
         shm_->world = (uint32_t)world;
         std::atomic_thread_fence(std::memory_order_release);
@@ -115,17 +115,43 @@ int Rendezvous::stage_barrier(uint32_t s, double timeout_s) {
 
 int Rendezvous::add_export(const unsigned char handle[64], uint64_t size) {
     RdvRank& me = self();
-    const uint32_t id = me.n_exports.load(std::memory_order_relaxed);
-    if (id >= (uint32_t)kRdvMaxExports) return -1;
-    memcpy(me.exports[id].handle, handle, 64);
-    me.exports[id].size = size;
-    me.exports[id].freed.store(0, std::memory_order_relaxed);
-    me.n_exports.store(id + 1, std::memory_order_release);
+    uint32_t id;
+    if (n_free_slots_ > 0) {
+        id = free_slots_[--n_free_slots_];
+    } else {
+        id = me.n_exports.load(std::memory_order_relaxed);
+        if (id >= (uint32_t)kRdvMaxExports) return -1;
+    }
+    RdvExport& x = me.exports[id];
+    memcpy(x.handle, handle, 64);
+    x.size = size;
+    x.generation++;
+    x.acks.store(0, std::memory_order_relaxed);
+    x.freed.store(0, std::memory_order_release);
+    if (id >= me.n_exports.load(std::memory_order_relaxed)) me.n_exports.store(id + 1, std::memory_order_release);
     return (int)id;
 }
 
 void Rendezvous::mark_freed(uint32_t export_id) {
-    if (shm_ && export_id < (uint32_t)kRdvMaxExports) self().exports[export_id].freed.store(1, std::memory_order_release);
+    if (!shm_ || export_id >= (uint32_t)kRdvMaxExports) return;
+    self().exports[export_id].freed.store(1, std::memory_order_release);
+    self().free_epoch.fetch_add(1, std::memory_order_release);
+}
+
+bool Rendezvous::released_by_all(uint32_t export_id) {
+    if (!shm_ || export_id >= (uint32_t)kRdvMaxExports) return true;
+    const uint32_t everyone = ((1u << world_) - 1) & ~(1u << rank_);
+    return (self().exports[export_id].acks.load(std::memory_order_acquire) & everyone) == everyone;
+}
+
+void Rendezvous::recycle(uint32_t export_id) {
+    if (shm_ && export_id < (uint32_t)kRdvMaxExports && n_free_slots_ < (uint32_t)kRdvMaxExports)
+        free_slots_[n_free_slots_++] = export_id;
+}
+
+void Rendezvous::ack_freed(int r, uint32_t export_id) {
+    if (shm_ && export_id < (uint32_t)kRdvMaxExports)
+        peer(r).exports[export_id].acks.fetch_or(1u << rank_, std::memory_order_acq_rel);
 }
 
 int Rendezvous::arrive(uint64_t k, const RdvSegment* table, uint32_t nseg, double timeout_s) {

@@ -61,8 +61,9 @@ def ptr_array(bufs):
 
 
 def sim_step(world, ns, p, g, m, v, wd, hyper, step, adam=True, mode=0, blocks_per_rank=0, timeout_ms=0,
-             active_mask=None):
-    """p, g, m, v: [rank][segment] DevBuf lists. Returns (rc, [status per rank])."""
+             active_mask=None, sumsq=None):
+    """p, g, m, v: [rank][segment] DevBuf lists. Returns (rc, [status per rank]). `sumsq`: a float64 array of
+    shape (world, segments) that receives, per rank, the sums of squares of the mean (two-shot, adam=False)."""
     nseg = len(ns)
     flat = lambda xs: ptr_array([xs[r][s] for r in range(world) for s in range(nseg)])  # noqa: E731
     status = (C.c_int * world)()
@@ -71,5 +72,6 @@ def sim_step(world, ns, p, g, m, v, wd, hyper, step, adam=True, mode=0, blocks_p
     rc = lib.slb_sim_step(world, nseg, longs(ns), flat(p) if adam else none, flat(g), flat(m) if adam else none,
                           flat(v) if adam else none, wd_arr, hyper["lr"], hyper["b1"], hyper["b2"], hyper["eps"], step,
                           1 if adam else 0, mode, blocks_per_rank, timeout_ms,
-                          (1 << world) - 1 if active_mask is None else active_mask, status)
+                          (1 << world) - 1 if active_mask is None else active_mask, status,
+                          sumsq.ctypes.data if sumsq is not None else None)
     return rc, list(status)

@@ -48,15 +48,8 @@ def test_config0_flat_buffer_matches_oracle_and_golden(cuda):
     assert max_rel(got[0][::s], gold["p"]) <= 1e-6
 
 
-@pytest.fixture(params=[0, 1], ids=["k_twoshot", "k_step"])
-def large_kernel(request):
-    set_option("pipeline", request.param)
-    yield request.param
-    set_option("pipeline", -1)
-
-
 @pytest.mark.parametrize("skew", [0, 1, 3])
-def test_ragged_tensors_in_one_launch_over_three_steps(cuda, skew, large_kernel):
+def test_ragged_tensors_in_one_launch_over_three_steps(cuda, skew):
     # empty-ish, sub-tile, tile-boundary and multi-tile sizes; skew != 0 makes pointers 4- but not 16-byte aligned
     sizes = [1, 3, 4, 5, 255, 2047, 2048, 2049, 4096 + 7, 100000, 3 * 2048]
     wds = [0.0 if i % 3 == 0 else 0.1 for i in range(len(sizes))]

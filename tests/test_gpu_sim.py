@@ -38,12 +38,12 @@ def oracle_steps(p0, g_by_step, sizes, wds, world):
     return ref, means
 
 
-@pytest.fixture(params=[0, 1], ids=["k_twoshot", "k_step"])
+@pytest.fixture(params=[0, 1, 2], ids=["loads-on-demand", "register-ring", "shared-memory-ring"])
 def large_kernel(request):
-    """Runs a test once with each of the two kernels that take large steps."""
-    set_option("pipeline", request.param)
+    """Runs a test once with each way the two-shot kernel can run its peer loads ahead of the arithmetic."""
+    set_option("prefetch", request.param)
     yield request.param
-    set_option("pipeline", -1)
+    set_option("prefetch", 2)
 
 
 @pytest.mark.parametrize("mode", [1, 2], ids=["oneshot", "twoshot"])
@@ -132,3 +132,24 @@ def test_missing_rank_makes_waits_run_out_and_the_device_stays_usable(cuda, larg
     assert rc == 0 and status == [0, 0]
     ref, _ = oracle_steps(p0, [g0], [5000], [0.1], world)
     np.testing.assert_array_equal(p[1][0].get(), ref[0][0])
+
+
+@pytest.mark.parametrize("world", [2, 3, 4, 5, 8])
+def test_two_shot_mean_leaves_the_sum_of_squares_of_every_tensor(cuda, world, large_kernel):
+    """The clip that follows a gradient mean needs sum(x^2) per tensor of the MEAN; the owner of each chunk has it in
+    registers. Every rank must end up with the same bits, equal to the oracle's piece-wise restatement."""
+    sizes = SIZES + [2048 * 37, 9, 2048 * 3]
+    for skew, blocks in ((0, 0), (0, 3), (1, 2)):
+        _, g0, p, g, m, v = make_case(world, sizes, seed=9, skew=skew)
+        got = np.zeros((world, len(sizes)), np.float64)
+        rc, status = sim_step(world, sizes, p, g, m, v, [0.0] * len(sizes), H, 1, adam=False, mode=2,
+                              blocks_per_rank=blocks, sumsq=got)
+        assert rc == 0 and status == [0] * world
+        means = [pyoracle.mean_ranks([g0[r][s] for r in range(world)]) for s in range(len(sizes))]
+        want = pyoracle.sumsq_pieces(means, world, counter("last_blocks"), vec=(skew == 0))
+        for r in range(world):
+            for s in range(len(sizes)):
+                np.testing.assert_array_equal(g[r][s].get(), means[s])
+            assert list(got[r]) == want, (r, list(got[r]), want)
+        exact = [float(np.sum(x.astype(np.float64) ** 2)) for x in means]
+        np.testing.assert_allclose(want, exact, rtol=1e-13)

@@ -29,6 +29,28 @@ def test_rendezvous_between_processes(lib, world):
     assert not os.path.exists(buf.raw[8:].split(b"\0")[0].decode())  # rank 0 removed the file
 
 
+def _slot_selftest(rank, world, id_bytes, q):
+    from soliton_b200._C import lib
+    q.put((rank, lib.slb_rdv_slot_selftest(ctypes.create_string_buffer(id_bytes, 128), rank, world, 150, 64)))
+
+
+def test_export_slots_are_reused_once_every_peer_has_let_go(lib):
+    """A trainer that returns its gradient blocks to the driver every step publishes new allocations for ever; the
+    table has 8192 slots per rank. 150 cycles x 64 allocations = 9600 pass through 64 slots."""
+    world = 3
+    buf = ctypes.create_string_buffer(128)
+    assert lib.slb_rdv_create_id(buf) == 0
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_slot_selftest, args=(r, world, buf.raw, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = dict(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(timeout=30)
+    assert results == {r: 0 for r in range(world)}
+
+
 def test_missing_rank_times_out_instead_of_hanging(lib):
     buf = ctypes.create_string_buffer(128)
     assert lib.slb_rdv_create_id(buf) == 0
