@@ -1,8 +1,10 @@
 """Benchmark of the data-parallel optimizer path: gradient mean over ranks + 1/world scaling + AdamW, fused.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--model 124M|medium] [--flat BYTES]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference|reference-gpu] [--model 124M|medium]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
         bench.py --gpus N --steps K --warmup W
+    python bench.py --fabric --gpus N          # what the NVLink fabric itself delivers (one process, all GPUs)
+    python bench.py --sweep --gpus N           # bucket sizes 4 KB .. 1 GB, one-shot against two-shot
 
 Workload: the GPT-2 124M parameter set (148 tensors, 124,439,808 fp32 parameters; soliton_b200/workload.py),
 parameters seeded as the reference's example initialises them, per-rank gradients N(0, 1e-3) seeded by rank,
@@ -11,15 +13,21 @@ all tensors through the Soliton-shaped Python interface: distributed.all_reduce_
 Inputs (2 GB per rank) are far larger than L2, so nothing is flushed between iterations.
 
 Prints ONE JSON line on rank 0. `value` is GB/s of algorithmic HBM traffic (28 bytes per parameter per rank: read
-g, p, m, v; write p, m, v) summed over all ranks, inputs resident in HBM. `e2e` is the same metric with, inside the
-timed region of every step, the host->device copy of the step's gradients from pinned memory and the device->host
-read of the updated parameters. `--impl reference` times the reference's host path (CPU restatement of
+g, p, m, v; write p, m, v) summed over all ranks, inputs resident in HBM; the timed region of K steps is repeated
+and the median reported, with the spread beside it. `e2e` is the same metric for a host-fed step: inside the timed
+region every step uploads its gradients from pinned host memory and reads the updated parameters back, bucket by
+bucket over the library's copy streams, and ends when the parameters are on the host. `parity` is one checked run of
+the same kernels on a small tensor set, against the CPU oracle bit for bit and across ranks by hash. `gpu_baseline`
+is the reference's own GPU path (grouped ncclAllReduce(avg) + one k_adamw launch per tensor, built unmodified into
+oracle/_ref/) timed in the same job. `--impl reference` times the reference's host path (CPU restatement of
 core/soliton/cpu.d: axpy per rank, scale, adamw; the D core cannot be built here) on the host cores.
 """
 import argparse
 import ctypes
+import hashlib
 import json
 import os
+import statistics
 import subprocess
 import sys
 import threading
@@ -28,29 +36,41 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+METRIC = "fused_allreduce_adamw_algorithmic_GBps"
 BYTES_PER_PARAM = 28            # algorithmic HBM bytes per parameter per rank
-NVLINK_GBS = 770.0              # measured peer copy bandwidth per direction on this pool (nominal 900)
+NVLINK_NOMINAL_GBS = 900.0      # per direction per GPU
+# What `bench.py --fabric` measured on this pool's 8 x B200 boxes when every GPU exchanges with every other at once
+# (GB/s received per GPU, the slowest GPU): by a kernel pulling with 256-bit loads, and by the copy engines.
+# None: not measured yet for that world size.
+FABRIC_MEASURED_GBS = {2: None, 4: None, 8: None}
 FALLBACK_HBM_GBS = 6650.0       # used only when MEASURED_PEAKS.json is absent
-# DRAM bytes per parameter of the dominant kernel from an ncu capture (profiles/), per world size; None = not captured
-NCU_DRAM_BYTES_PER_PARAM = {1: 27.22}  # profiles/k_twoshot_w1_flat256MiB_ncu.md
+# DRAM bytes per parameter of the dominant kernel from an ncu capture, per world size; None = not captured
+NCU_DRAM_BYTES_PER_PARAM = {1: 27.22}
+# A small tensor set for the checked run: 1.6 M floats, above the one-shot staging slot at every world size
+PARITY_SHAPES = [(1000, 1200), (1200,), (300, 1000), (1000,), (3,), (2048 * 50,)]
 
 
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-gpu"])
     ap.add_argument("--model", default="124M", choices=["124M", "medium", "tiny"])
     ap.add_argument("--flat", type=int, default=0, help="one flat buffer of this many bytes instead of a model")
+    ap.add_argument("--regions", type=int, default=5, help="how often the timed region of --steps steps is repeated")
     ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--bucket-mb", type=int, default=32, help="bucket size of the host-fed step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-gpu-baseline", action="store_true")
     ap.add_argument("--mode", type=int, default=0, help="0 auto, 1 one-shot, 2 two-shot")
     ap.add_argument("--blocks-per-sm", type=int, default=0)
     ap.add_argument("--cyclic", type=int, default=-1)
+    ap.add_argument("--prefetch", type=int, default=-1, help="two-shot peer loads: 0 on demand, 1 register ring, 2 shared-memory ring")
+    ap.add_argument("--stamps", action="store_true", help="device times at the phase borders of the last launch")
     ap.add_argument("--sweep", action="store_true", help="bucket-size sweep 4 KB .. 1 GB, one-shot vs two-shot (N >= 2)")
+    ap.add_argument("--fabric", action="store_true", help="NVLink fabric ceiling: copy engines and kernels, one and both directions")
     ap.add_argument("--bare", action="store_true", help="gradient mean only, no optimizer update (link-bound floor)")
-    ap.add_argument("--pipeline", type=int, default=-1, help="-1 auto, 1 k_step (shared-memory ring), 0 k_twoshot")
     return ap.parse_args()
 
 
@@ -135,96 +155,285 @@ class ClockSampler:
                 "samples": len(sm), "source": "nvidia-smi"}
 
 
+def workload_name(args):
+    if args.flat:
+        return f"flat fp32 buffer, {args.flat} bytes"
+    from soliton_b200 import workload
+    return f"GPT-2 {args.model} parameter set, {len(workload.param_shapes(args.model))} tensors"
+
+
 def make_workload(args):
-    """[(name, shape)] and per-rank host arrays (params identical on all ranks, gradients seeded by rank)."""
-    import numpy as np
+    """Shapes and per-rank host arrays (params identical on all ranks, gradients seeded by rank). A flat buffer is
+    given the shape (1, n): a matrix, so that it takes weight decay as BASELINE's flat configurations say."""
     from soliton_b200 import workload
     if args.flat:
         n = args.flat // 4
-        shapes = [("flat", (n,))]
-        make_p = lambda: [workload.flat_case(n)[0]]                                  # noqa: E731
-        make_g = lambda rank: [workload.flat_case(n, rank=rank)[1]]                  # noqa: E731
-        wds = [workload.HYPER["wd"]]
-        name = f"flat fp32 buffer, {args.flat} bytes"
+        shapes = [(1, n)]
+        make_p = lambda: [workload.flat_case(n)[0].reshape(1, n)]                        # noqa: E731
+        make_g = lambda rank: [workload.flat_case(n, rank=rank)[1].reshape(1, n)]        # noqa: E731
     else:
-        ps = workload.param_shapes(args.model)
-        shapes = [(nm, s) for nm, s, _ in ps]
-        make_p = lambda: workload.init_params(args.model, seed=0)                    # noqa: E731
-        make_g = lambda rank: workload.rank_grads(args.model, rank=rank)             # noqa: E731
-        wds = [workload.HYPER["wd"] if len(s) >= 2 else 0.0 for _, s in shapes]
-        name = f"GPT-2 {args.model} parameter set, {len(shapes)} tensors"
-    return shapes, make_p, make_g, wds, name, np
+        shapes = [s for _, s, _ in workload.param_shapes(args.model)]
+        make_p = lambda: workload.init_params(args.model, seed=0)                        # noqa: E731
+        make_g = lambda rank: workload.rank_grads(args.model, rank=rank)                 # noqa: E731
+    return shapes, make_p, make_g
+
+
+def total_params(args):
+    from soliton_b200 import workload
+    return args.flat // 4 if args.flat else workload.total_params(args.model)
+
+
+def host_path_seconds(args, world, steps, threads):
+    """Seconds for `steps` steps of the reference's host path over the WHOLE workload on each of `threads` threads
+    (one thread stands for one rank's process: the reference's host kernels are single-threaded loops)."""
+    import numpy as np
+    from oracle import pyoracle
+    n = total_params(args)
+    p0 = np.random.default_rng(0).standard_normal(n, dtype=np.float32) * np.float32(0.02)
+    grads = [np.random.default_rng(1 + r).standard_normal(n, dtype=np.float32) * np.float32(1e-3) for r in range(world)]
+    return pyoracle.bench(p0, grads, steps, threads), n
 
 
 def run_reference(args, rank, world):
-    """The reference's host path (restated; core/soliton/cpu.d:85-101,362-373) on the host cores: every one of
-    `world` threads, standing for one rank's process, sums the ranks' gradients, scales and runs AdamW."""
+    """The reference's host path (restated; core/soliton/cpu.d:85-101,362-373) on the host cores, over the same
+    parameter set as the GPU arm: every one of `world` threads, standing for one rank's process, sums the ranks'
+    gradients, scales and runs AdamW."""
     if rank != 0:
         return
-    import numpy as np
-    from oracle import pyoracle
-    from soliton_b200 import workload
-    total = args.flat // 4 if args.flat else workload.total_params(args.model)
-    n = min(total, 4 << 20)  # bounded sample of the workload: its first 4 Mi parameters
-    p0 = np.random.default_rng(0).standard_normal(n, dtype=np.float32) * np.float32(0.02)
-    grads = [np.random.default_rng(1 + r).standard_normal(n, dtype=np.float32) * np.float32(1e-3) for r in range(world)]
     cores = min(world, os.cpu_count() or 1)
-    pyoracle.bench(p0, grads, max(args.warmup, 1), cores)
-    t = pyoracle.bench(p0, grads, args.steps, cores)
+    host_path_seconds(args, world, max(args.warmup, 1), cores)
+    t, n = host_path_seconds(args, world, args.steps, cores)
     ms = 1e3 * t / args.steps
     value = cores * BYTES_PER_PARAM * n / (t / args.steps) / 1e9
-    name = f"flat fp32 buffer, {args.flat} bytes" if args.flat else f"GPT-2 {args.model} parameter set"
     line = {
-        "impl": "reference", "metric": "fused_allreduce_adamw_algorithmic_GBps", "value": value, "unit": "GB/s",
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": name, "params_per_rank": total, "world": world},
+        "config": {"workload": workload_name(args), "params_per_rank": n, "world": world},
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": "port",
-                         "sample": f"first {n} parameters per step, {args.steps} steps, one thread per rank "
+                         "sample": f"all {n} parameters per step, {args.steps} steps, one thread per rank "
                                    f"(the reference's host kernels are single-threaded loops)"},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
 
 
-def cpu_baseline(world):
-    """Rank 0, N = 1: the host path on one core over a bounded sample, about ten seconds of CPU work."""
+def cpu_baseline(args):
+    """Rank 0, N = 1: the host path on one core over the whole parameter set, about ten seconds of CPU work."""
+    t1, n = host_path_seconds(args, 1, 2, 1)
+    reps = max(3, min(50, int(10.0 / max(t1 / 2, 1e-4))))
+    t, n = host_path_seconds(args, 1, reps, 1)
+    return {"value": BYTES_PER_PARAM * n * reps / t / 1e9, "unit": "GB/s", "cores": 1, "kind": "port",
+            "sample": f"all {n} parameters, {reps} steps, single thread as in core/soliton/cpu.d",
+            "ms_per_step": 1e3 * t / reps, "host_cores_available": os.cpu_count()}
+
+
+def bind_near_gpu(lib, ordinal):
+    """Keeps this process (and the pages of the pinned buffers it allocates next) on the NUMA node the GPU hangs on,
+    so that eight ranks feeding eight GPUs do not pull each other's host memory across the socket link."""
+    try:
+        buf = ctypes.create_string_buffer(32)
+        if lib.slb_device_pci_bus_id(ordinal, buf, 32) != 0:
+            return None
+        node = int(open(f"/sys/bus/pci/devices/{buf.value.decode().lower()}/numa_node").read())
+        if node < 0:
+            return None
+        cpus = set()
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = os.sched_getaffinity(0) & cpus
+        if not allowed:
+            return None
+        os.sched_setaffinity(0, allowed)
+        return node
+    except Exception:
+        return None
+
+
+class Pinned:
+    """float32 buffer in page-locked host memory from the library."""
+
+    def __init__(self, lib, n):
+        import numpy as np
+        self.lib, self.ptr = lib, lib.slb_pinned_alloc(4 * n)
+        if not self.ptr:
+            raise MemoryError("pinned host allocation failed")
+        self.array = np.ctypeslib.as_array(ctypes.cast(self.ptr, ctypes.POINTER(ctypes.c_float)), shape=(n,))
+
+    def data_ptr(self):
+        return self.ptr
+
+
+def reference_gpu_lib():
+    from oracle import build as obuild
+    if not os.path.exists(obuild.REF_SO):
+        return None
+    C = ctypes
+    R = C.CDLL(obuild.REF_SO)
+    R.sl_cuda_malloc.restype = C.c_void_p
+    R.sl_cuda_malloc.argtypes = [C.c_size_t]
+    R.sl_cuda_free.argtypes = [C.c_void_p]
+    R.sl_cuda_h2d.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
+    R.sl_cuda_adamw.argtypes = [C.c_void_p] * 4 + [C.c_int64] + [C.c_float] * 5 + [C.c_int]
+    R.sl_cuda_nccl_allreduce_mean.argtypes = [C.c_void_p, C.c_int64]
+    R.sl_cuda_fill.argtypes = [C.c_void_p, C.c_int64, C.c_float]
+    return R
+
+
+def time_reference_gpu(args, R, rank, local_rank, world, dist, steps, warmup):
+    """ms per step (max over ranks) of the reference's own GPU path on this box: grouped ncclAllReduce(avg) per tensor,
+    then one k_adamw launch per tensor (core/cuda/kernels.cu:242-254,772-775)."""
+    import numpy as np
+    import torch
+    from soliton_b200 import workload
+    C = ctypes
+    assert R.sl_cuda_set_device(local_rank) == 0
+    if world > 1:
+        idt = torch.zeros(128, dtype=torch.uint8, device="cuda")
+        if rank == 0:
+            buf = C.create_string_buffer(128)
+            assert R.sl_cuda_nccl_unique_id(buf) == 0
+            idt.copy_(torch.frombuffer(bytearray(buf.raw), dtype=torch.uint8))
+        dist.broadcast(idt, 0)
+        assert R.sl_cuda_nccl_init(rank, world, C.create_string_buffer(bytes(idt.cpu().numpy().tobytes()), 128)) == 0
+    shapes, make_p, make_g = make_workload(args)
+    H = workload.HYPER
+    bufs = []
+    for a, gr in zip(make_p(), make_g(rank)):
+        n = int(a.size)
+        ptrs = [R.sl_cuda_malloc(4 * n) for _ in range(4)]
+        R.sl_cuda_h2d(ptrs[0], np.ascontiguousarray(a).ctypes.data, 4 * n)
+        R.sl_cuda_h2d(ptrs[1], np.ascontiguousarray(gr).ctypes.data, 4 * n)
+        R.sl_cuda_fill(ptrs[2], n, 0.0)
+        R.sl_cuda_fill(ptrs[3], n, 0.0)
+        bufs.append((ptrs, n, H["wd"] if len(a.shape) >= 2 else 0.0))
+    t = [0]
+
+    def step():
+        t[0] += 1
+        if world > 1:
+            R.sl_cuda_nccl_group(1)
+            for ptrs, n, _ in bufs:
+                R.sl_cuda_nccl_allreduce_mean(ptrs[1], n)
+            R.sl_cuda_nccl_group(0)
+        for ptrs, n, wd in bufs:
+            R.sl_cuda_adamw(ptrs[0], ptrs[1], ptrs[2], ptrs[3], n, H["lr"], H["b1"], H["b2"], H["eps"], wd, t[0])
+
+    for _ in range(max(warmup, 3)):
+        step()
+    R.sl_cuda_sync()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    R.sl_cuda_sync()
+    ms = torch.tensor([e0.elapsed_time(e1) / steps], device="cuda")
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    assert R.sl_cuda_check() == 0
+    if world > 1:
+        R.sl_cuda_nccl_destroy()
+    for ptrs, _, _ in bufs:
+        for p in ptrs:
+            R.sl_cuda_free(p)
+    return float(ms.item()), len(bufs) + (1 if world > 1 else 0)
+
+
+def nccl_version():
+    try:
+        import torch
+        return ".".join(str(x) for x in torch.cuda.nccl.version())
+    except Exception:
+        return None
+
+
+def parity_check(rank, world, dist):
+    """One checked run of the path on a small tensor set: two steps through the same calls as the timed region, then
+    every rank compares parameters, moments and gradients with the CPU oracle bit for bit, and the ranks compare a
+    hash of their parameters."""
     import numpy as np
     from oracle import pyoracle
-    n = 4 << 20
-    p0 = np.random.default_rng(0).standard_normal(n, dtype=np.float32) * np.float32(0.02)
-    grads = [np.random.default_rng(1 + r).standard_normal(n, dtype=np.float32) * np.float32(1e-3) for r in range(world)]
-    t1 = pyoracle.bench(p0, grads, 2, 1)
-    reps = max(3, min(400, int(10.0 / max(t1 / 2, 1e-4))))
-    t = pyoracle.bench(p0, grads, reps, 1)
-    return {"value": BYTES_PER_PARAM * n * reps / t / 1e9, "unit": "GB/s", "cores": 1, "kind": "port",
-            "sample": f"first {n} parameters, {reps} steps, single thread as in core/soliton/cpu.d",
-            "host_cores_available": os.cpu_count()}
+    from soliton_b200 import distributed, tensor as T, workload
+    from soliton_b200._C import counter
+    from soliton_b200.optim import AdamW
+    H = workload.HYPER
+    shapes = PARITY_SHAPES
+    p0 = [(np.random.default_rng(100 + i).standard_normal(s) * 0.02).astype(np.float32) for i, s in enumerate(shapes)]
+    grads = lambda r, step: [(np.random.default_rng(1000 * step + 10 * r + i).standard_normal(s) * 1e-3).astype(np.float32)  # noqa: E731
+                             for i, s in enumerate(shapes)]
+    params = [T.tensor(a, "cuda") for a in p0]
+    opt = AdamW(params, lr=H["lr"], betas=(H["b1"], H["b2"]), eps=H["eps"], weight_decay=H["wd"])
+    ref = [[a.ravel().copy(), np.zeros(a.size, np.float32), np.zeros(a.size, np.float32)] for a in p0]
+    ok = True
+    for step in (1, 2):
+        for p, g in zip(params, grads(rank, step)):
+            p.grad = T.tensor(g, "cuda")
+        distributed.all_reduce_grads(opt.params)
+        opt.step()
+        T.synchronize()
+        mode = counter("last_mode")
+        per_rank = [grads(r, step) for r in range(world)]
+        for i, s in enumerate(shapes):
+            mean = pyoracle.mean_ranks([per_rank[r][i].ravel() for r in range(world)])
+            pyoracle.adamw(ref[i][0], mean, ref[i][1], ref[i][2], H["lr"], H["b1"], H["b2"], H["eps"],
+                           H["wd"] if len(s) >= 2 else 0.0, step, fma=True)
+            ok = ok and np.array_equal(params[i].grad.numpy().ravel(), mean)
+            ok = ok and np.array_equal(params[i].numpy().ravel(), ref[i][0])
+            ok = ok and np.array_equal(opt.state[i][0].numpy().ravel(), ref[i][1])
+            ok = ok and np.array_equal(opt.state[i][1].numpy().ravel(), ref[i][2])
+        opt.zero_grad()
+    digest = hashlib.sha256(b"".join(p.numpy().tobytes() for p in params)).hexdigest()
+    all_ok, digests = [ok], [digest]
+    if world > 1:
+        all_ok, digests = [None] * world, [None] * world
+        dist.all_gather_object(all_ok, ok)
+        dist.all_gather_object(digests, digest)
+    return {"vs_oracle_bits": bool(all(all_ok)), "cross_rank_hash_equal": len(set(digests)) == 1, "world": world,
+            "kernel": {0: "k_twoshot<1,adam>", 1: f"k_oneshot<{world},adam>", 2: f"k_twoshot<{world},adam>"}[mode],
+            "tensors": len(shapes), "params": int(sum(a.size for a in p0)), "steps": 2, "sha256_p": digest[:16]}
 
 
 def run_ours(args, rank, local_rank, world):
+    import numpy as np
     import torch
     import torch.distributed as dist
     torch.cuda.set_device(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    from soliton_b200 import distributed, tensor as T
+    from soliton_b200 import distributed, tensor as T, workload
     from soliton_b200._C import counter, lib, set_option
+    from soliton_b200.bucketed import BucketedAdamW
     from soliton_b200.optim import AdamW
-    from soliton_b200 import workload
-    shapes, make_p, make_g, wds, name, np = make_workload(args)
     H = workload.HYPER
+    numa = bind_near_gpu(lib, local_rank)
 
     T.set_device(local_rank)
     T._dev(T.CUDA)
-    if args.mode:
-        set_option("mode", args.mode)
-    if args.blocks_per_sm:
-        set_option("blocks_per_sm", args.blocks_per_sm)
-    if args.pipeline >= 0:
-        set_option("pipeline", args.pipeline)
-    if args.cyclic >= 0:
-        set_option("cyclic", args.cyclic)
+    for name, value in (("mode", args.mode), ("blocks_per_sm", args.blocks_per_sm)):
+        if value:
+            set_option(name, value)
+    for name, value in (("cyclic", args.cyclic), ("prefetch", args.prefetch)):
+        if value >= 0:
+            set_option(name, value)
+    if args.stamps:
+        set_option("stamps", 1)
+
+    # the same-box GPU baseline first: the reference's own NCCL + k_adamw path, in this job, on this workload
+    gpu_baseline = None
+    if not args.no_gpu_baseline and not args.bare:
+        R = reference_gpu_lib()
+        if R is None:
+            gpu_baseline = {"unavailable": "oracle/_ref/ not built (no reference checkout at build time)"}
+        else:
+            ms_ref, launches_ref = time_reference_gpu(args, R, rank, local_rank, world, dist, 10, 3)
+            gpu_baseline = {"kind": "reference ncclAllReduce(avg) grouped + one k_adamw per tensor, oracle/_ref",
+                            "ms_per_step": ms_ref, "launches_per_step": launches_ref, "nccl": nccl_version(), "steps": 10}
+
     if world > 1:
         idt = torch.zeros(128, dtype=torch.uint8, device="cuda")
         if rank == 0:
@@ -232,34 +441,31 @@ def run_ours(args, rank, local_rank, world):
         dist.broadcast(idt, 0)
         distributed.init_with_id(rank, world, bytes(idt.cpu().numpy().tobytes()))
 
+    parity = parity_check(rank, world, dist)
+
     # device state through the library's allocator; host copies of the gradients in pinned memory for the e2e leg
+    shapes, make_p, make_g = make_workload(args)
     host_p = make_p()
     host_g = make_g(rank)
     P = sum(int(a.size) for a in host_p)
     params = [T.tensor(a, "cuda") for a in host_p]
-    pinned_g = [torch.empty(a.size, dtype=torch.float32).pin_memory() for a in host_g]
-    for t, a in zip(pinned_g, host_g):
-        t.numpy()[:] = a.ravel()
-    pinned_out = [torch.empty(a.size, dtype=torch.float32).pin_memory() for a in host_p]
+    pinned_g = [Pinned(lib, int(a.size)) for a in host_g]
+    for buf, a in zip(pinned_g, host_g):
+        buf.array[:] = a.ravel()
+    pinned_out = [Pinned(lib, int(a.size)) for a in host_p]
     for p, a in zip(params, host_g):
         p.grad = T.tensor(a, "cuda")
     del host_p, host_g
 
-    class Opt(AdamW):  # weight decay per tensor as the workload defines it (flat buffers decay although 1-D)
-        def step(self):
-            self.t += 1
-            b1, b2 = self.betas
-            for (p, (m, v)), wd in zip(zip(self.params, self.state), wds):
-                lib.sl_adamw(p.dev, p.ptr, p.grad.ptr, m.ptr, v.ptr, p.numel, self.lr, b1, b2, self.eps, wd, self.t)
-
-    opt = Opt(params, lr=H["lr"], betas=(H["b1"], H["b2"]), eps=H["eps"], weight_decay=H["wd"])
+    opt = BucketedAdamW(params, bucket_bytes=args.bucket_mb << 20, lr=H["lr"], betas=(H["b1"], H["b2"]), eps=H["eps"],
+                        weight_decay=H["wd"])
 
     def step():
         distributed.all_reduce_grads(opt.params)
         if args.bare:
             lib.slb_flush()
         else:
-            opt.step()
+            AdamW.step(opt)   # the whole step as one launch
 
     def fence():
         lib.slb_flush()
@@ -289,69 +495,101 @@ def run_ours(args, rank, local_rank, world):
     if rank == 0:
         sampler.start()
     launches0 = counter("launches")
-    total_ms = timed(args.steps, step)
-    launches = counter("launches") - launches0
+    region_ms = [timed(args.steps, step) / args.steps for _ in range(max(args.regions, 1))]
+    launches = (counter("launches") - launches0) // max(args.regions, 1)
     clocks = sampler.stop() if rank == 0 else None
     err = lib.sl_check(T.CUDA)
     if err:
         raise RuntimeError(f"soliton_b200: sticky error {err} after the timed region")
     mode, blocks = counter("last_mode"), counter("last_blocks")
+    stamps = None
+    if args.stamps and world > 1:
+        raw = (ctypes.c_uint64 * 5)()
+        if lib.slb_read_stamps(raw) == 0:
+            t = [int(x) for x in raw]
+            stamps = {"us_wait_for_peers": (t[1] - t[0]) / 1e3, "us_reduce_own_chunk": (t[2] - t[1]) / 1e3,
+                      "us_gather_other_chunks": (t[3] - t[2]) / 1e3, "us_wait_peers_done": (t[4] - t[3]) / 1e3,
+                      "us_total_block0": (t[4] - t[0]) / 1e3}
 
-    def e2e_step():
-        for p, src in zip(params, pinned_g):
-            lib.sl_from_host(T.CUDA, p.grad.ptr, src.data_ptr(), p.numel * 4)
-        step()
-        for p, dst in zip(params, pinned_out):
-            lib.sl_to_host(T.CUDA, dst.data_ptr(), p.ptr, p.numel * 4)
+    # host-fed step: gradients up, parameters down, bucket by bucket over the copy streams
+    opt.bind_host(pinned_g, pinned_out)
+    e2e_ms, breakdown = None, None
+    if not args.bare:
+        opt.host_step()
+        e2e_ms = timed(args.e2e_steps, opt.host_step) / args.e2e_steps
 
-    e2e_step()
-    e2e_ms = timed(args.e2e_steps, e2e_step)
+        def uploads():
+            for b in range(len(opt.buckets)):
+                opt.upload(b)
+            lib.slb_wait_copies()
+
+        def downloads():
+            for b in range(len(opt.buckets)):
+                opt.download(b)
+            lib.slb_wait_copies()
+
+        breakdown = {"h2d_ms": timed(2, uploads) / 2, "d2h_ms": timed(2, downloads) / 2, "kernel_ms": statistics.median(region_ms),
+                     "buckets": len(opt.buckets), "numa_node": numa}
+        if world > 1:
+            per_rank = [None] * world
+            dist.all_gather_object(per_rank, {"rank": rank, "numa_node": numa})
+            breakdown["ranks"] = per_rank
+    err = lib.sl_check(T.CUDA)
+    if err:
+        raise RuntimeError(f"soliton_b200: sticky error {err} after the host-fed steps")
 
     if rank != 0:
         if world > 1:
             distributed.destroy()
             dist.destroy_process_group()
         return
-    ms = total_ms / args.steps
+    ms = statistics.median(region_ms)
     value = world * BYTES_PER_PARAM * P / (ms * 1e-3) / 1e9
-    e2e_value = world * BYTES_PER_PARAM * P / (e2e_ms / args.e2e_steps * 1e-3) / 1e9
     hbm, hbm_kind = hbm_peak()
     hbm_per_rank = BYTES_PER_PARAM * P / (ms * 1e-3) / 1e9
     t_hbm = BYTES_PER_PARAM * P / (hbm * 1e9)
     nvl_bytes = 8.0 * P * (world - 1) / world
-    t_nvl = nvl_bytes / (NVLINK_GBS * 1e9)
-    per_launch_ms = total_ms / max(launches, 1)
-    use_step = args.pipeline == 1
-    base = "k_step" if use_step else "k_twoshot"
-    kernel = {0: f"{base}<1,adam>", 1: f"k_oneshot<{world},adam>", 2: f"{base}<{world},adam>"}[mode]
+    fabric = FABRIC_MEASURED_GBS.get(world)
+    t_nvl = nvl_bytes / (NVLINK_NOMINAL_GBS * 1e9)
+    kernel = {0: "k_twoshot<1,adam>", 1: f"k_oneshot<{world},adam>", 2: f"k_twoshot<{world},adam>"}[mode]
+    if args.bare:
+        kernel = kernel.replace(",adam>", ",mean only>")
     traffic = NCU_DRAM_BYTES_PER_PARAM.get(world)
     if t_hbm >= t_nvl:
         roof = {"bound": "hbm", "achieved": hbm_per_rank, "peak": hbm, "unit": "GB/s", "frac": hbm_per_rank / hbm,
-                "traffic": traffic * P if traffic else None}
+                "traffic": traffic * P if traffic else None, "peak_source": f"{hbm_kind} HBM copy"}
     else:
         nvl = nvl_bytes / (ms * 1e-3) / 1e9
-        roof = {"bound": "nvlink", "achieved": nvl, "peak": NVLINK_GBS, "unit": "GB/s", "frac": nvl / NVLINK_GBS,
-                "traffic": traffic * P if traffic else None, "hbm_achieved": hbm_per_rank, "hbm_peak": hbm,
-                "hbm_frac": hbm_per_rank / hbm}
-    roof.update({"kernel": kernel, "peak_source": f"{hbm_kind} HBM copy; NVLink 770 GB/s measured peer copy",
-                 "ms_per_launch": per_launch_ms, "roofline_ms": 1e3 * max(t_hbm, t_nvl),
+        roof = {"bound": "nvlink", "achieved": nvl, "peak": NVLINK_NOMINAL_GBS, "unit": "GB/s", "frac": nvl / NVLINK_NOMINAL_GBS,
+                "traffic": traffic * P if traffic else None, "peak_source": "nominal NVLink 5, per direction per GPU",
+                "fabric_measured": fabric, "frac_of_fabric_measured": nvl / fabric["sm_pull"] if fabric else None,
+                "hbm_achieved": hbm_per_rank, "hbm_peak": hbm, "hbm_frac": hbm_per_rank / hbm}
+    roof.update({"kernel": kernel, "ms_per_launch": ms / max(launches / args.steps, 1), "roofline_ms": 1e3 * max(t_hbm, t_nvl),
                  "frac_of_roofline_time": max(t_hbm, t_nvl) / (ms * 1e-3)})
     line = {
-        "metric": "fused_allreduce_adamw_algorithmic_GBps", "value": value, "unit": "GB/s", "n_gpus": world,
+        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": name, "params_per_rank": P, "world": world, "l2": "inputs larger than L2, no flush",
+        "config": {"workload": workload_name(args), "params_per_rank": P, "world": world,
+                   "l2": "inputs larger than L2, no flush",
                    "exchange": {0: "none", 1: "one-shot", 2: "two-shot"}[mode], "blocks_per_rank": blocks,
                    "optimizer": "none (--bare)" if args.bare else "AdamW",
                    "arithmetic": "gradient mean, m, v in f32; parameter update in f64, rounded to f32 once",
-                   "e2e_copies": "h2d: this step's gradients from pinned memory; d2h: updated parameters"},
-        "roofline": roof,
-        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": 4 * P, "d2h_bytes_per_step": 4 * P,
-                "ms_per_step": e2e_ms / args.e2e_steps, "steps": args.e2e_steps},
+                   "e2e_copies": "h2d: this step's gradients from pinned memory; d2h: updated parameters; "
+                                 f"buckets of {args.bucket_mb} MiB over two copy streams beside the kernels"},
+        "regions": {"n": len(region_ms), "steps_each": args.steps, "ms_per_step_median": ms,
+                    "ms_per_step_min": min(region_ms), "ms_per_step_max": max(region_ms)},
+        "roofline": roof, "parity": parity, "gpu_baseline": gpu_baseline,
         "gpu_launches": int(launches), "clocks": clocks,
     }
+    if e2e_ms is not None:
+        line["e2e"] = {"value": world * BYTES_PER_PARAM * P / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
+                       "h2d_bytes_per_step": 4 * P, "d2h_bytes_per_step": 4 * P, "ms_per_step": e2e_ms,
+                       "steps": args.e2e_steps, "breakdown": breakdown}
+    if stamps:
+        line["phases_block0_last_launch"] = stamps
     if world == 1 and not args.no_cpu_baseline:
-        line["cpu_baseline"] = cpu_baseline(1)
+        line["cpu_baseline"] = cpu_baseline(args)
     print(json.dumps(line), flush=True)
     if world > 1:
         distributed.destroy()
@@ -424,86 +662,51 @@ def run_sweep(args, rank, local_rank, world):
     dist.destroy_process_group()
 
 
+def run_fabric(args):
+    """One process, all GPUs: GB/s per GPU that the fabric delivers to copy engines and to kernels, with every link
+    carrying data one way and both ways. The slowest GPU's figure is the ceiling a collective can be held against."""
+    from soliton_b200._C import lib
+    have = lib.sl_cuda_count()
+    rows = []
+    nbytes = 64 << 20
+    for w in (2, 4, 8):
+        if w > min(have, args.gpus):
+            continue
+        for mode, name in ((0, "copy engines"), (1, "kernel, 256-bit loads (pull)"), (2, "kernel, 256-bit stores (push)")):
+            for both in (0, 1):
+                gbs = (ctypes.c_double * 8)()
+                ms = (ctypes.c_double * 8)()
+                rc = lib.slb_fabric_probe(w, nbytes, mode, both, 20, gbs, ms)
+                active = [round(g, 1) for g in list(gbs)[:w] if g > 0]
+                rows.append({"gpus": w, "by": name, "links": "both directions at once" if both else "one direction",
+                             "rc": rc, "GBps_per_gpu_min": min(active) if active else None,
+                             "GBps_per_gpu_max": max(active) if active else None,
+                             "ms": round(max(list(ms)[:w]), 2), "bytes_per_pair": nbytes, "repeats": 20})
+    print(json.dumps({"metric": "nvlink_fabric_GBps_per_direction_per_gpu", "gpus_visible": have, "rows": rows}), flush=True)
+
+
 def run_reference_gpu(args, rank, local_rank, world):
-    """The reference's own GPU path on this box: grouped ncclAllReduce(avg) per tensor, then one k_adamw launch per
-    tensor (core/cuda/kernels.cu:242-254,772-775), from the unmodified backend built into oracle/_ref/."""
-    import ctypes as C
+    """The reference's own GPU path as an arm of its own (the product arm also carries it as `gpu_baseline`)."""
     import torch
     import torch.distributed as dist
-    from oracle import build as obuild
-    if not os.path.exists(obuild.REF_SO):
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    R = reference_gpu_lib()
+    if R is None:
         if rank == 0:
             print(json.dumps({"impl": "reference-gpu", "unavailable": "oracle/_ref/ not built (no reference checkout at build time)"}))
         return
-    torch.cuda.set_device(local_rank)
-    if world > 1:
-        dist.init_process_group("gloo")
-    R = C.CDLL(obuild.REF_SO)
-    assert R.sl_cuda_set_device(local_rank) == 0
-    R.sl_cuda_malloc.restype = C.c_void_p
-    R.sl_cuda_malloc.argtypes = [C.c_size_t]
-    R.sl_cuda_h2d.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
-    R.sl_cuda_adamw.argtypes = [C.c_void_p] * 4 + [C.c_int64] + [C.c_float] * 5 + [C.c_int]
-    R.sl_cuda_nccl_allreduce_mean.argtypes = [C.c_void_p, C.c_int64]
-    R.sl_cuda_fill.argtypes = [C.c_void_p, C.c_int64, C.c_float]
-    if world > 1:
-        idt = torch.zeros(128, dtype=torch.uint8)
-        if rank == 0:
-            buf = C.create_string_buffer(128)
-            assert R.sl_cuda_nccl_unique_id(buf) == 0
-            idt = torch.frombuffer(bytearray(buf.raw), dtype=torch.uint8).clone()
-        dist.broadcast(idt, 0)
-        assert R.sl_cuda_nccl_init(rank, world, C.create_string_buffer(bytes(idt.numpy().tobytes()), 128)) == 0
-    shapes, make_p, make_g, wds, name, np = make_workload(args)
-    from soliton_b200 import workload
-    H = workload.HYPER
-    bufs = []
-    for a, gr in zip(make_p(), make_g(rank)):
-        n = int(a.size)
-        ptrs = [R.sl_cuda_malloc(4 * n) for _ in range(4)]
-        R.sl_cuda_h2d(ptrs[0], np.ascontiguousarray(a).ctypes.data, 4 * n)
-        R.sl_cuda_h2d(ptrs[1], np.ascontiguousarray(gr).ctypes.data, 4 * n)
-        R.sl_cuda_fill(ptrs[2], n, 0.0)
-        R.sl_cuda_fill(ptrs[3], n, 0.0)
-        bufs.append((ptrs, n))
-    P = sum(n for _, n in bufs)
-    t = [0]
-
-    def step():
-        t[0] += 1
-        if world > 1:
-            R.sl_cuda_nccl_group(1)
-            for ptrs, n in bufs:
-                R.sl_cuda_nccl_allreduce_mean(ptrs[1], n)
-            R.sl_cuda_nccl_group(0)
-        for (ptrs, n), wd in zip(bufs, wds):
-            R.sl_cuda_adamw(ptrs[0], ptrs[1], ptrs[2], ptrs[3], n, H["lr"], H["b1"], H["b2"], H["eps"], wd, t[0])
-
-    for _ in range(max(args.warmup, 3)):
-        step()
-    R.sl_cuda_sync()
-    if world > 1:
-        dist.barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    R.sl_cuda_sync()
-    ms = torch.tensor([e0.elapsed_time(e1) / args.steps])
-    if world > 1:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    assert R.sl_cuda_check() == 0
+    ms, launches = time_reference_gpu(args, R, rank, local_rank, world, dist, args.steps, args.warmup)
+    P = total_params(args)
     if rank == 0:
-        m = float(ms.item())
-        print(json.dumps({"impl": "reference-gpu", "metric": "fused_allreduce_adamw_algorithmic_GBps",
-                          "value": world * BYTES_PER_PARAM * P / (m * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": world,
-                          "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": m, "higher_is_better": True,
-                          "config": {"workload": name, "params_per_rank": P, "world": world,
+        print(json.dumps({"impl": "reference-gpu", "metric": METRIC,
+                          "value": world * BYTES_PER_PARAM * P / (ms * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": world,
+                          "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+                          "config": {"workload": workload_name(args), "params_per_rank": P, "world": world,
                                      "path": "reference core/cuda/kernels.cu: grouped ncclAllReduce(avg) + k_adamw per tensor"},
-                          "gpu_launches_per_step": len(bufs) + (1 if world > 1 else 0)}), flush=True)
+                          "nccl": nccl_version(), "gpu_launches_per_step": launches}), flush=True)
     if world > 1:
-        R.sl_cuda_nccl_destroy()
         dist.destroy_process_group()
 
 
@@ -512,6 +715,8 @@ def main():
     rank = int(os.environ.get("RANK", 0))
     local_rank = int(os.environ.get("LOCAL_RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
+    if args.fabric:
+        return run_fabric(args)
     if world == 1 and args.gpus > 1:
         # launched without torchrun: start one process per GPU ourselves
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",

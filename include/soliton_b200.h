@@ -191,6 +191,18 @@ int slb_rdv_create_id(char* out128);
  * by `world` processes without CUDA, `cycles` x `per_cycle` fake allocations per rank. 0 when everything matched
  * and no more than per_cycle slots were ever in use. */
 int slb_rdv_slot_selftest(const char* id128, int rank, int world, int cycles, int per_cycle);
+/* Measurement, no counterpart in the reference: what the NVLink fabric of this box delivers when `ngpus` GPUs move
+ * `bytes` per pair at once, driven from this one process. mode 0: copy engines (cudaMemcpyPeerAsync); 1: a kernel on
+ * the receiver pulling with 256-bit loads; 2: a kernel on the sender pushing with 256-bit stores. both_directions 0:
+ * the lower half of the GPUs receives from the upper half (every link one way only); 1: every GPU exchanges with
+ * every other (every link both ways at once, as in an all-reduce). gbs_per_gpu[ngpus] (and ms_per_gpu, may be NULL)
+ * receive, for every GPU that issued work, GB/s received (modes 0, 1) or sent (mode 2) and its device time.
+ * 0, -1 bad argument, -2 fewer GPUs than asked, -3 a CUDA call failed or peer access is not available. */
+int slb_fabric_probe(int ngpus, size_t bytes, int mode, int both_directions, int repeats, double* gbs_per_gpu,
+                     double* ms_per_gpu);
+/* PCI address of a device ("0000:1b:00.0"), for callers that want to place their host buffers on the NUMA node the
+ * GPU hangs on (/sys/bus/pci/devices/<address>/numa_node). 0 or -1. */
+int slb_device_pci_bus_id(int ordinal, char* out, int len);
 /* Page-locked host memory for slb_from_host_async / slb_to_host_async (cudaHostAlloc). NULL on failure. */
 void* slb_pinned_alloc(size_t n);
 void slb_pinned_free(void* p);

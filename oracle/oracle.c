@@ -203,11 +203,13 @@ double oracle_bench(const float* p0, const float* const* g, int world, int64_t n
     for (int t = 0; t < threads; t++) {
         bench_arg* a = &args[t];
         a->p = (float*)malloc((size_t)n * 4);
-        a->m = (float*)calloc((size_t)n, 4);
-        a->v = (float*)calloc((size_t)n, 4);
+        a->m = (float*)malloc((size_t)n * 4);
+        a->v = (float*)malloc((size_t)n * 4);
         a->acc = (float*)malloc((size_t)n * 4);
         if (!a->p || !a->m || !a->v || !a->acc) return -1;
         memcpy(a->p, p0, (size_t)n * 4);
+        /* every page is touched before the clock starts: the steady state of a training loop, not its first step */
+        memset(a->m, 0, (size_t)n * 4), memset(a->v, 0, (size_t)n * 4), memset(a->acc, 0, (size_t)n * 4);
         a->g = g, a->world = world, a->n = n, a->reps = reps, a->seconds = 0;
     }
     for (int t = 0; t < threads; t++)

@@ -328,6 +328,14 @@ int slb_rdv_slot_selftest(const char* id128, int rank, int world, int cycles, in
     return rc;
 }
 
+int slb_device_pci_bus_id(int ordinal, char* out, int len) {
+    if (!out || len < 16 || cudaDeviceGetPCIBusId(out, len, ordinal) != cudaSuccess) {
+        cudaGetLastError();
+        return -1;
+    }
+    return 0;
+}
+
 void* slb_pinned_alloc(size_t n) {
     void* p = nullptr;
     if (cudaHostAlloc(&p, n ? n : 1, cudaHostAllocPortable) != cudaSuccess) {

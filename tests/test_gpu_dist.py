@@ -68,7 +68,7 @@ def worker(rank, world, init_file, outdir, case, steps, with_ref, clip=0.0, use_
             assert T.memory_stats("cuda")["reserved"] - reserved0 == plan.bytes
         params = [T.tensor(a, "cuda") for a in params_for(shapes)]
         opt = AdamW(params, lr=H["lr"], betas=(H["b1"], H["b2"]), eps=H["eps"], weight_decay=H["wd"])
-        modes, launches, norms = [], [], []
+        modes, launches, norms, blocks = [], [], [], []
         ref_state = None
         if with_ref:
             from oracle import build as obuild
@@ -117,13 +117,14 @@ def worker(rank, world, init_file, outdir, case, steps, with_ref, clip=0.0, use_
             if clip:
                 from soliton_b200.optim import clip_grad_norm
                 norms.append(clip_grad_norm(opt.params, clip))
+                blocks.append(counter("last_blocks"))   # of the gradient mean, which the clip's first question launched
             opt.step()
             T.synchronize()
             launches.append(counter("launches") - before)
             modes.append(counter("last_mode"))
             last_g = [p.grad.numpy() for p in params]
             opt.zero_grad()
-        out = {"modes": np.array(modes), "launches": np.array(launches), "norms": np.array(norms)}
+        out = {"modes": np.array(modes), "launches": np.array(launches), "norms": np.array(norms), "blocks": np.array(blocks)}
         for i, (p, (m, v)) in enumerate(zip(params, opt.state)):
             out[f"p{i}"], out[f"m{i}"], out[f"v{i}"], out[f"g{i}"] = p.numpy(), m.numpy(), v.numpy(), last_g[i]
         if with_ref:
@@ -208,7 +209,7 @@ def test_arena_mode_one_exported_block_per_rank(cuda, world):
 
 
 @pytest.mark.parametrize("world", [2, 8])
-def test_clipped_step_matches_oracle_and_is_three_launches(cuda, world):
+def test_clipped_step_matches_oracle_and_is_two_launches(cuda, world):
     """all_reduce_grads -> clip_grad_norm -> step, as examples/gpt2.py:92-94 of the reference runs it."""
     if n_gpus() < world:
         pytest.skip(f"needs {world} GPUs")
@@ -221,6 +222,9 @@ def test_clipped_step_matches_oracle_and_is_three_launches(cuda, world):
         per_rank = [grads_for(r, step, shapes) for r in range(world)]
         means = [pyoracle.mean_ranks([per_rank[r][i].ravel() for r in range(world)]) for i in range(len(shapes))]
         norm = math.sqrt(sum(pyoracle.sumsq(g) for g in means))
+        blocks = int(res[0]["blocks"][step - 1])
+        pieces = math.sqrt(sum(pyoracle.sumsq_pieces(means, world, blocks)))
+        assert float(res[0]["norms"][step - 1]) == pieces   # the oracle's piece-wise restatement, every bit
         for r in range(world):
             assert res[r]["norms"][step - 1] == pytest.approx(norm, rel=1e-12)
             assert res[r]["norms"][step - 1] == res[0]["norms"][step - 1]   # every rank computes the same norm bits
@@ -232,7 +236,8 @@ def test_clipped_step_matches_oracle_and_is_three_launches(cuda, world):
             pyoracle.adamw(state[i][0], means[i], state[i][1], state[i][2], H["lr"], H["b1"], H["b2"], H["eps"],
                            H["wd"] if len(s) >= 2 else 0.0, step, fma=True)
     for r in range(world):
-        assert list(res[r]["launches"]) == [3] * steps   # all-reduce, batched sumsq, AdamW with the scale folded in
+        # the mean leaves the sum of squares of what it produced: no separate pass; AdamW applies the scale
+        assert list(res[r]["launches"]) == [2] * steps
         for i in range(len(shapes)):
             np.testing.assert_array_equal(res[r][f"g{i}"].ravel(), means[i])
             np.testing.assert_array_equal(res[r][f"p{i}"].ravel(), state[i][0])
@@ -273,3 +278,152 @@ def test_against_reference_nccl_and_k_adamw(cuda, world):
                 assert np.all(np.abs(a - b) <= bound), float(np.max(np.abs(a - b) - bound))
             np.testing.assert_allclose(g, rg, rtol=1e-6, atol=1e-6 * np.max(np.abs(rg)))
     print(f"world {world}: {strict_fail} elements outside the element-wise 1e-6 (summation-order cancellation)")
+
+
+def worker_bucketed(rank, world, init_file, outdir, steps):
+    """Buckets in reverse parameter order, each reduced and stepped as soon as its gradients exist, on the library's
+    own stream beside the legacy stream."""
+    try:
+        from soliton_b200 import distributed, tensor as T
+        from soliton_b200._C import counter, set_option
+        from soliton_b200.bucketed import BucketedAdamW
+        shapes = CASES["large"]
+        distributed.init(rank, world, init_file, timeout=120)
+        set_option("overlap", 1)
+        params = [T.tensor(a, "cuda") for a in params_for(shapes)]
+        opt = BucketedAdamW(params, bucket_bytes=1 << 20, lr=H["lr"], betas=(H["b1"], H["b2"]), eps=H["eps"], weight_decay=H["wd"])
+        launches, modes = [], []
+        for step in range(1, steps + 1):
+            gs = grads_for(rank, step, shapes)
+            before = counter("launches")
+            opt.begin_step()
+            for b, bucket in enumerate(opt.buckets):
+                for i in bucket:
+                    params[i].grad = T.tensor(gs[i], "cuda")
+                opt.step_bucket(b)
+                modes.append(counter("last_mode"))
+            launches.append(counter("launches") - before)
+            last_g = [p.grad.numpy() for p in params]
+            opt.zero_grad()
+        T.synchronize()
+        out = {"launches": np.array(launches), "buckets": np.array(len(opt.buckets)), "modes": np.array(modes)}
+        for i, (p, (m, v)) in enumerate(zip(params, opt.state)):
+            out[f"p{i}"], out[f"m{i}"], out[f"v{i}"], out[f"g{i}"] = p.numpy(), m.numpy(), v.numpy(), last_g[i]
+        np.savez(os.path.join(outdir, f"rank{rank}.npz"), **out)
+        distributed.destroy()
+    except BaseException as e:
+        import traceback
+        with open(os.path.join(outdir, f"rank{rank}.err"), "w") as f:
+            f.write("".join(traceback.format_exception(e)))
+        raise
+
+
+def worker_backend(rank, world, init_file, outdir, steps):
+    """Only what a Soliton build binds: sl_cuda_dp_set_workspace, sl_cuda_nccl_*, sl_cuda_adamw, on memory from
+    plain cudaMalloc (the library finds the allocations through the driver)."""
+    try:
+        import ctypes as C
+        import time
+        from soliton_b200._C import lib as L
+        from tests.cudart import Cudart
+        rt = Cudart()
+        rt.set_device(rank)
+        ws_bytes = L.slb_workspace_bytes()
+        assert L.sl_cuda_dp_set_workspace(rt.malloc(ws_bytes), ws_bytes) == 0
+        idbuf = C.create_string_buffer(128)
+        if rank == 0:
+            assert L.sl_cuda_nccl_unique_id(idbuf) == 0
+            with open(init_file + ".tmp", "wb") as f:
+                f.write(idbuf.raw)
+            os.replace(init_file + ".tmp", init_file)
+        else:
+            t0 = time.time()
+            while not os.path.exists(init_file):
+                assert time.time() - t0 < 120
+                time.sleep(0.05)
+            C.memmove(idbuf, open(init_file, "rb").read(128), 128)
+        assert L.sl_cuda_nccl_init(rank, world, idbuf) == 0
+        shapes = CASES["large"]
+        host_p = params_for(shapes)
+        dev = []
+        for a in host_p:
+            ptrs = [rt.malloc(a.nbytes) for _ in range(4)]          # p, m, v, g
+            rt.h2d(ptrs[0], np.ascontiguousarray(a))
+            zero = np.zeros(a.size, np.float32)
+            rt.h2d(ptrs[1], zero), rt.h2d(ptrs[2], zero)
+            dev.append(ptrs)
+        for step in range(1, steps + 1):
+            for ptrs, g in zip(dev, grads_for(rank, step, shapes)):
+                rt.h2d(ptrs[3], np.ascontiguousarray(g))
+            assert L.sl_cuda_nccl_group(1) == 0
+            for ptrs, a in zip(dev, host_p):
+                assert L.sl_cuda_nccl_allreduce_mean(ptrs[3], a.size) == 0
+            assert L.sl_cuda_nccl_group(0) == 0
+            for ptrs, a, s in zip(dev, host_p, shapes):
+                L.sl_cuda_adamw(ptrs[0], ptrs[3], ptrs[1], ptrs[2], a.size, H["lr"], H["b1"], H["b2"], H["eps"],
+                                H["wd"] if len(s) >= 2 else 0.0, step)
+            L.slb_flush()
+            rt.sync()
+        assert L.sl_check(2) == 0
+        out = {}
+        for i, (ptrs, a) in enumerate(zip(dev, host_p)):
+            for name, ptr in zip("pmvg", ptrs):
+                got = np.empty(a.size, np.float32)
+                rt.d2h(got, ptr)
+                out[f"{name}{i}"] = got
+        np.savez(os.path.join(outdir, f"rank{rank}.npz"), **out)
+        L.sl_cuda_nccl_destroy()
+    except BaseException as e:
+        import traceback
+        with open(os.path.join(outdir, f"rank{rank}.err"), "w") as f:
+            f.write("".join(traceback.format_exception(e)))
+        raise
+
+
+def run_workers(target, world, *args):
+    outdir = tempfile.mkdtemp()
+    init_file = os.path.join(outdir, "group_id")
+    ctx = mp.get_context("spawn")
+    procs = [ctx.Process(target=target, args=(r, world, init_file, outdir, *args)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=300)
+    for p in procs:
+        if p.is_alive():
+            p.kill()
+    errs = [open(os.path.join(outdir, f)).read() for f in sorted(os.listdir(outdir)) if f.endswith(".err")]
+    assert not errs, "\n".join(errs)
+    return [dict(np.load(os.path.join(outdir, f"rank{r}.npz"))) for r in range(world)]
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_bucketed_steps_on_their_own_stream_match_oracle(cuda, world):
+    if n_gpus() < world:
+        pytest.skip(f"needs {world} GPUs")
+    steps = 4
+    res = run_workers(worker_bucketed, world, steps)
+    state, means = oracle_run(world, "large", steps)
+    for r in range(world):
+        nb = int(res[r]["buckets"])
+        assert nb >= 2 and list(res[r]["launches"]) == [nb] * steps     # one fused launch per bucket
+        for i in range(len(CASES["large"])):
+            np.testing.assert_array_equal(res[r][f"g{i}"].ravel(), means[i])
+            np.testing.assert_array_equal(res[r][f"p{i}"].ravel(), state[i][0])
+            np.testing.assert_array_equal(res[r][f"m{i}"].ravel(), state[i][1])
+            np.testing.assert_array_equal(res[r][f"v{i}"].ravel(), state[i][2])
+
+
+@pytest.mark.parametrize("world", [2])
+def test_backend_level_entry_points_across_processes(cuda, world):
+    if n_gpus() < world:
+        pytest.skip(f"needs {world} GPUs")
+    steps = 3
+    res = run_workers(worker_backend, world, steps)
+    state, means = oracle_run(world, "large", steps)
+    for r in range(world):
+        for i in range(len(CASES["large"])):
+            np.testing.assert_array_equal(res[r][f"g{i}"], means[i])
+            np.testing.assert_array_equal(res[r][f"p{i}"], state[i][0])
+            np.testing.assert_array_equal(res[r][f"m{i}"], state[i][1])
+            np.testing.assert_array_equal(res[r][f"v{i}"], state[i][2])

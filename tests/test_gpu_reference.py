@@ -79,6 +79,33 @@ def test_special_values_bit_identical_to_reference_kernel(ref):
             np.testing.assert_array_equal(a.get().view(np.uint32), b.get().view(np.uint32))
 
 
+def test_overflowing_second_moment_bit_identical_to_reference_kernel(ref):
+    # |g| above about 1.8e19: (1 - b2) * g * g overflows float, v becomes +inf. IEEE arithmetic then gives
+    # sqrt(inf) = inf and m / (inf + eps) = 0, so p only sees the weight decay; an infinite gradient gives NaN.
+    n = 4096 + 17
+    rng = np.random.default_rng(23)
+    p0 = (rng.standard_normal(n) * 0.02).astype(np.float32)
+    g0 = (rng.standard_normal(n) * 1e-3).astype(np.float32)
+    g0[::5] = 1e20
+    g0[1::7] = -3e25
+    g0[2::11] = np.float32(3.0e38)
+    g0[3::13] = np.inf
+    g0[4::17] = -np.inf
+    h = dict(lr=3e-4, b1=0.9, b2=0.999, eps=1e-8, wd=0.1)
+    g = DevBuf(g0)
+    ours, theirs = [DevBuf(p0), zeros(n), zeros(n)], [DevBuf(p0), zeros(n), zeros(n)]
+    for step in (1, 2):
+        lib.sl_adamw(CUDA, ours[0].ptr, g.ptr, ours[1].ptr, ours[2].ptr, n, h["lr"], h["b1"], h["b2"], h["eps"], h["wd"], step)
+        check_ok()
+        ref.sl_cuda_adamw(theirs[0].ptr, g.ptr, theirs[1].ptr, theirs[2].ptr, n, h["lr"], h["b1"], h["b2"], h["eps"], h["wd"], step)
+        ref.sl_cuda_sync()
+        for a, b in zip(ours, theirs):
+            x, y = a.get(), b.get()
+            both_nan = np.isnan(x) & np.isnan(y)       # NaN payloads are not part of the contract
+            np.testing.assert_array_equal(np.where(both_nan, 0, x).view(np.uint32), np.where(both_nan, 0, y).view(np.uint32))
+        assert np.isfinite(ours[0].get()[::5]).all()   # overflowed v, finite m: the parameter stays finite
+
+
 def test_config0_against_reference_kernel(ref):
     n = 1 << 20
     p0, g0 = workload.flat_case(n)
