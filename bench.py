@@ -61,6 +61,7 @@ def parse():
     ap.add_argument("--regions", type=int, default=5, help="how often the timed region of --steps steps is repeated")
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--bucket-mb", type=int, default=32, help="bucket size of the host-fed step")
+    ap.add_argument("--wc", action="store_true", help="write-combined pinned memory for the upload sources")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-gpu-baseline", action="store_true")
     ap.add_argument("--mode", type=int, default=0, help="0 auto, 1 one-shot, 2 two-shot")
@@ -254,9 +255,9 @@ def bind_near_gpu(lib, ordinal):
 class Pinned:
     """float32 buffer in page-locked host memory from the library."""
 
-    def __init__(self, lib, n):
+    def __init__(self, lib, n, write_combined=False):
         import numpy as np
-        self.lib, self.ptr = lib, lib.slb_pinned_alloc(4 * n)
+        self.lib, self.ptr = lib, (lib.slb_pinned_alloc_wc if write_combined else lib.slb_pinned_alloc)(4 * n)
         if not self.ptr:
             raise MemoryError("pinned host allocation failed")
         self.array = np.ctypeslib.as_array(ctypes.cast(self.ptr, ctypes.POINTER(ctypes.c_float)), shape=(n,))
@@ -449,7 +450,7 @@ def run_ours(args, rank, local_rank, world):
     host_g = make_g(rank)
     P = sum(int(a.size) for a in host_p)
     params = [T.tensor(a, "cuda") for a in host_p]
-    pinned_g = [Pinned(lib, int(a.size)) for a in host_g]
+    pinned_g = [Pinned(lib, int(a.size), write_combined=args.wc) for a in host_g]
     for buf, a in zip(pinned_g, host_g):
         buf.array[:] = a.ravel()
     pinned_out = [Pinned(lib, int(a.size)) for a in host_p]

@@ -205,6 +205,8 @@ int slb_fabric_probe(int ngpus, size_t bytes, int mode, int both_directions, int
 int slb_device_pci_bus_id(int ordinal, char* out, int len);
 /* Page-locked host memory for slb_from_host_async / slb_to_host_async (cudaHostAlloc). NULL on failure. */
 void* slb_pinned_alloc(size_t n);
+/* The same, write-combined: for buffers the host only ever writes (upload sources); reading them on the host is slow. */
+void* slb_pinned_alloc_wc(size_t n);
 void slb_pinned_free(void* p);
 
 #ifdef __cplusplus

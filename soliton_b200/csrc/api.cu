@@ -22,6 +22,8 @@ static inline void before_release(int dev, const void* p, size_t n) {
     if (dev == DEV_CUDA && E().cuda_ready()) E().before_release(p, n);  // nor may work in flight on another stream
 }
 
+extern "C" int slb_foreign_check(void) __attribute__((weak));
+
 extern "C" {
 
 // ---- memory
@@ -80,7 +82,9 @@ void sl_arena_off(int dev) {
 int sl_init_device(int dev, int ordinal) { return E().init_device(dev, ordinal); }
 int sl_cuda_count(void) { return E().device_count(); }
 int sl_check(int dev) {
-    const int e = E().check();
+    int e = E().check();
+    // a build that serves the rest of Soliton's ABI from another backend folds that backend's sticky error in here
+    if (!e && dev == DEV_CUDA && slb_foreign_check) e = slb_foreign_check();
     return dev == DEV_CUDA || e == ERR_NO_CPU_COMPUTE ? e : 0;
 }
 void sl_sync(int dev) {
@@ -339,6 +343,14 @@ int slb_device_pci_bus_id(int ordinal, char* out, int len) {
 void* slb_pinned_alloc(size_t n) {
     void* p = nullptr;
     if (cudaHostAlloc(&p, n ? n : 1, cudaHostAllocPortable) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    return p;
+}
+void* slb_pinned_alloc_wc(size_t n) {
+    void* p = nullptr;
+    if (cudaHostAlloc(&p, n ? n : 1, cudaHostAllocPortable | cudaHostAllocWriteCombined) != cudaSuccess) {
         cudaGetLastError();
         return nullptr;
     }

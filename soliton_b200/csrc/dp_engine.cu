@@ -255,7 +255,9 @@ int Engine::init_device(int dev, int ordinal) {
     if (dev == DEV_CPU) return 0;
     if (!valid_dev(dev)) return -1;
     if (dev == DEV_CUDA && bind_device(ordinal) != 0) return -1;
-    if (!pool(dev).alloc(kBlasWorkspace)) return -2;  // api.d:110 OOM code
+    void* blas = pool(dev).alloc(kBlasWorkspace);
+    if (!blas) return -2;  // api.d:110 OOM code
+    if (dev == DEV_CUDA) blas_ws_ = blas;
     void* ws = pool(dev).alloc(kWorkspaceBytes);
     if (!ws) return -2;
     if (dev == DEV_CUDA && adopt_workspace(ws, kWorkspaceBytes) != 0) return -1;

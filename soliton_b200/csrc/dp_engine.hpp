@@ -123,6 +123,11 @@ public:
     int adopt_workspace(void* p, size_t n);
     bool cuda_ready() const { return ws_ != nullptr; }
     char* workspace() const { return ws_; }
+    int ordinal() const { return ordinal_; }
+    // The 32 MiB the reference reserves for cuBLAS at device initialisation (core/soliton/api.d:129,268-272): this
+    // library has no use for it, a backend that serves the rest of the ABI does.
+    void* blas_workspace() const { return blas_ws_; }
+    size_t blas_workspace_bytes() const { return blas_ws_ ? size_t(32) << 20 : 0; }
 
     // --- the path
     void adamw(float* p, const float* g, float* m, float* v, int64_t n, float lr, float b1, float b2, float eps,
@@ -195,6 +200,7 @@ private:
     int err_ = 0;
     int ordinal_ = 0, sm_count_ = 0;
     char* ws_ = nullptr;
+    void* blas_ws_ = nullptr;
     int* status_host_ = nullptr;    // kMaxWorld ints, host-mapped; [0] is the real rank's
     int* status_dev_ = nullptr;
     Lanes lanes_;

@@ -107,8 +107,7 @@ __device__ __forceinline__ void st_plain8(float* p, const float8& v) {
 // The operands here are floats promoted to double and bias corrections in (0, 1], far from the exponent limits,
 // so the checked range is not needed. Each routine ends in FMA residual corrections that make the result the
 // correctly rounded one (Markstein's construction); the GPU tests compare every bit with IEEE division / sqrt.
-// Infinite operands (a second moment that overflowed float) would turn the Newton steps into NaN; they are passed
-// through by a select at the end of each routine, with the value IEEE arithmetic gives.
+// Operands must be finite: adamw_elem deals with an overflowed second moment before it gets here.
 __device__ __forceinline__ double rcp_seed(double d) {
     double y;
     asm("rcp.approx.ftz.f64 %0, %1;" : "=d"(y) : "d"(d));
@@ -119,15 +118,13 @@ __device__ __forceinline__ double rsqrt_seed(double x) {
     asm("rsqrt.approx.ftz.f64 %0, %1;" : "=d"(y) : "d"(x));
     return y;
 }
-__device__ __forceinline__ bool is_inf(double x) { return fabs(x) == __longlong_as_double(0x7ff0000000000000LL); }
-// a / b with y = RN(1 / b) supplied (b is a launch constant in (0, 1]; the host rounds its reciprocal correctly).
+// a / b with y = RN(1 / b) supplied (b is a launch constant; the host rounds its reciprocal correctly).
 __device__ __forceinline__ double div_by_const(double a, double b, double y) {
     double q = __dmul_rn(a, y);
     double r = __fma_rn(-b, q, a);
     q = __fma_rn(r, y, q);      // faithful
     r = __fma_rn(-b, q, a);
-    q = __fma_rn(r, y, q);      // correctly rounded
-    return is_inf(a) ? a : q;   // inf / b = inf for b > 0
+    return __fma_rn(r, y, q);   // correctly rounded
 }
 __device__ __forceinline__ double div_exact(double a, double d) {
     double y = rcp_seed(d);                     // ~20 bits
@@ -137,13 +134,7 @@ __device__ __forceinline__ double div_exact(double a, double d) {
     y = __fma_rn(y, e, y);                      // full precision, within an ulp
     e = __fma_rn(-d, y, 1.0);
     y = __fma_rn(y, e, y);                      // RN(1 / d)
-    double q = __dmul_rn(a, y);
-    double r = __fma_rn(-d, q, a);
-    q = __fma_rn(r, y, q);
-    r = __fma_rn(-d, q, a);
-    q = __fma_rn(r, y, q);
-    // d = +inf (d is a square root plus eps, never negative): finite / inf = signed zero, inf / inf = NaN
-    return is_inf(d) ? __dmul_rn(a, 0.0) : (is_inf(a) ? a : q);
+    return div_by_const(a, d, y);
 }
 __device__ __forceinline__ double sqrt_exact(double x) {
     const double y = rsqrt_seed(x);             // ~20 bits of 1 / sqrt(x)
@@ -156,19 +147,25 @@ __device__ __forceinline__ double sqrt_exact(double x) {
     g = __fma_rn(rem, h, g);
     rem = __fma_rn(-g, g, x);
     g = __fma_rn(rem, h, g);
-    return (x == 0.0 || is_inf(x)) ? x : g;     // the seed of 0 is inf and the seed of inf is 0; sqrt returns both as is
+    return x == 0.0 ? 0.0 : g;                  // the seed of 0 is inf; sqrt(0) is 0
 }
 
 // One element of the reference update (core/cuda/kernels.cu:242-250) with every rounding written out, so that the
 // result does not depend on how a compiler contracts the expression: m and v in float with the products feeding
 // an FMA, bias-corrected moments and the quotient in correctly rounded double, wd * p rounded in float before it
 // is promoted, one final rounding of p to float.
+// A gradient beyond about 1.8e19 overflows the float second moment to +inf. IEEE arithmetic then gives
+// sqrt(inf) = inf and m / (inf + eps) = a zero with the sign of m (NaN when m is infinite too), where the Newton
+// steps above would give NaN; that one case is decided on the float v and patched in with a select.
 __device__ __forceinline__ void adamw_elem(float& p, float g, float& m, float& v, const Hyper& h, float wd) {
     m = __fmaf_rn(h.b1, m, __fmul_rn(h.c1, g));
     v = __fmaf_rn(h.b2, v, __fmul_rn(__fmul_rn(h.c2, g), g));
     const double mh = div_by_const((double)m, h.bc1, h.rbc1);
     const double vh = div_by_const((double)v, h.bc2, h.rbc2);
-    const double x = __dadd_rn(div_exact(mh, __dadd_rn(sqrt_exact(vh), (double)h.eps)), (double)__fmul_rn(wd, p));
+    const double decay = (double)__fmul_rn(wd, p);
+    double x = __dadd_rn(div_exact(mh, __dadd_rn(sqrt_exact(vh), (double)h.eps)), decay);
+    const double x_overflowed = __dadd_rn((double)__fmul_rn(m, 0.0f), decay);
+    x = v == __int_as_float(0x7f800000) ? x_overflowed : x;
     p = __double2float_rn(__fma_rn(-(double)h.lr, x, (double)p));
 }
 __device__ __forceinline__ void adamw_vec(float4& p, const float4& g, float4& m, float4& v, const Hyper& h, float wd) {

@@ -103,7 +103,8 @@ def test_overflowing_second_moment_bit_identical_to_reference_kernel(ref):
             x, y = a.get(), b.get()
             both_nan = np.isnan(x) & np.isnan(y)       # NaN payloads are not part of the contract
             np.testing.assert_array_equal(np.where(both_nan, 0, x).view(np.uint32), np.where(both_nan, 0, y).view(np.uint32))
-        assert np.isfinite(ours[0].get()[::5]).all()   # overflowed v, finite m: the parameter stays finite
+        overflowed = np.abs(g0) == np.float32(1e20)
+        assert overflowed.any() and np.isfinite(ours[0].get()[overflowed]).all()   # v = inf, m finite: p stays finite
 
 
 def test_config0_against_reference_kernel(ref):
