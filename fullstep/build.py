@@ -74,8 +74,32 @@ def compile_reference_python():
     return True
 
 
+def _compiled_files():
+    found = []
+    for base, _, files in os.walk(OUT):
+        found += [os.path.join(base, f) for f in files if f.endswith(".pyc") or f.endswith(".pyc.bin")]
+    return found
+
+
+def keep_travel_copies():
+    """Tools that ship a source tree tend to leave *.pyc behind; every compiled file also exists as *.pyc.bin."""
+    for path in _compiled_files():
+        if path.endswith(".pyc") and _stale(path + ".bin", [path]):
+            shutil.copyfile(path, path + ".bin")
+
+
+def ensure_importable():
+    """Where only the *.pyc.bin copies arrived, puts the *.pyc files back. Called by everything that imports them."""
+    for path in _compiled_files():
+        if path.endswith(".pyc.bin") and not os.path.exists(path[:-4]):
+            shutil.copyfile(path, path[:-4])
+    return os.path.exists(os.path.join(PKG, "__init__.pyc"))
+
+
 def build(force=False):
-    return build_library(force), build_backend(), compile_reference_python()
+    out = build_library(force), build_backend(), compile_reference_python()
+    keep_travel_copies()
+    return out
 
 
 if __name__ == "__main__":

@@ -22,6 +22,7 @@
 #include <cstring>
 
 #include "../soliton_b200/csrc/dp_engine.hpp"
+#include "../soliton_b200/csrc/foreign_path.h"
 #include "../soliton_b200/csrc/pool.hpp"
 
 using namespace slb;
@@ -56,6 +57,9 @@ struct Backend {
                       float*, float*, float*, float*, float*, void*) = nullptr;
     void (*attention_bwd)(const float*, const float*, const float*, const float*, float*, int64_t, int64_t, int64_t,
                           int64_t, float, int64_t, float*, float*, float*, float*, float*, float*, float*, float*, void*) = nullptr;
+    // the reference's own data-parallel path and the small ops around it (core/cuda/kernels.cu:200-224,242-254,756-779)
+    SlbForeignPath dp{};
+    int (*nccl_unique_id)(char*) = nullptr;
     int (*jit)(const char*, const char*, void**) = nullptr;
     void (*jit_launch)(void*, int64_t, void**) = nullptr;
     void (*jit_free)(void*) = nullptr;
@@ -108,7 +112,12 @@ Backend& backend() {
                          bind(b.so, "sl_cuda_cross_entropy_bwd", b.cross_entropy_bwd) &
                          bind(b.so, "sl_cuda_attention", b.attention) & bind(b.so, "sl_cuda_attention_bwd", b.attention_bwd) &
                          bind(b.so, "sl_cuda_jit", b.jit) & bind(b.so, "sl_cuda_jit_launch", b.jit_launch) &
-                         bind(b.so, "sl_cuda_jit_free", b.jit_free) & bind(b.so, "sl_cuda_jit_log", b.jit_log);
+                         bind(b.so, "sl_cuda_jit_free", b.jit_free) & bind(b.so, "sl_cuda_jit_log", b.jit_log) &
+                         bind(b.so, "sl_cuda_adamw", b.dp.adamw) & bind(b.so, "sl_cuda_nccl_unique_id", b.dp.dist_unique_id) &
+                         bind(b.so, "sl_cuda_nccl_init", b.dp.dist_init) & bind(b.so, "sl_cuda_nccl_group", b.dp.dist_group) &
+                         bind(b.so, "sl_cuda_nccl_allreduce_mean", b.dp.dist_allreduce_mean) &
+                         bind(b.so, "sl_cuda_nccl_destroy", b.dp.dist_destroy) & bind(b.so, "sl_cuda_sumsq", b.dp.sumsq) &
+                         bind(b.so, "sl_cuda_scale", b.dp.scale) & bind(b.so, "sl_cuda_axpy", b.dp.axpy);
         if (!all) {
             dlclose(b.so);
             b.so = nullptr;
@@ -369,6 +378,18 @@ void sl_jit_free(int dev, void* handle) {
     if (dev == DEV_CUDA && backend().ok) backend().jit_free(handle);
 }
 const char* sl_jit_log(void) { return backend().ok ? backend().jit_log() : ""; }
+
+// SOLITON_FULLSTEP_DP=reference: the path's entry points go to the reference's own NCCL + k_adamw instead of this
+// library's kernels (see csrc/foreign_path.h). Everything else -- allocator, forward, backward -- stays as it is.
+const SlbForeignPath* slb_foreign_path(void) {
+    static const bool wanted = [] {
+        const char* v = getenv("SOLITON_FULLSTEP_DP");
+        return v && strcmp(v, "reference") == 0;
+    }();
+    if (!wanted) return nullptr;
+    Backend& b = backend();
+    return b.ok ? &b.dp : nullptr;
+}
 
 // The backend's own sticky error (core/cuda/kernels.cu:21,101-105), for the library's sl_check to fold in.
 int slb_foreign_check(void) {

@@ -24,6 +24,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 REF = os.path.join(HERE, "_ref")
 sys.path[:0] = [REF, ROOT]
+from fullstep.build import ensure_importable  # noqa: E402
+ensure_importable()
 
 V = 50257
 
@@ -39,9 +41,12 @@ def main():
     ap.add_argument("--budget-gib", type=float, default=0.0, help="solve recomputation so that the step fits this budget")
     ap.add_argument("--nproc", type=int, default=1)
     ap.add_argument("--hash", action="store_true")
+    ap.add_argument("--dp", default="ours", choices=["ours", "reference"],
+                    help="reference: gradient mean and AdamW on the reference's own NCCL + k_adamw instead of this library")
     ap.add_argument("--timeout", type=float, default=1500.0)
     args = ap.parse_args()
 
+    os.environ["SOLITON_FULLSTEP_DP"] = args.dp
     if args.nproc > 1 and "RANK" not in os.environ:
         from soliton_b200.launch import launch_workers
         sys.exit(launch_workers(args.nproc, [sys.executable, os.path.abspath(__file__), *sys.argv[1:]], timeout=args.timeout))
@@ -100,7 +105,7 @@ def main():
         digest = h.hexdigest()
     warm = times[2:] or times
     out = {"rank": rank, "world": world, "config": args.config, "batch_per_rank": args.batch, "seq": seq, "steps": args.steps,
-           "matmul": "tf32" if args.tf32 else "fp32", "allocator": "pool" if plan is None else "arena",
+           "matmul": "tf32" if args.tf32 else "fp32", "data_parallel_path": args.dp, "allocator": "pool" if plan is None else "arena",
            "recomputed_units": ckpt if isinstance(ckpt, int) else len(ckpt),
            "step_ms": 1000 * sum(warm) / len(warm), "tokens_per_s": args.batch * seq * world * len(warm) / sum(warm),
            "loss_first": losses[0], "loss_last": losses[-1], "plan_seconds": plan_s,

@@ -16,7 +16,9 @@ import traceback
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 REF = os.path.join(HERE, "_ref")
-sys.path[:0] = [REF, os.path.join(REF, "reftests")]   # what the reference's tests/conftest.py:4-5 puts on the path
+sys.path[:0] = [REF, os.path.join(REF, "reftests"), os.path.dirname(HERE)]   # the first two: what the reference's tests/conftest.py:4-5 puts on the path
+from fullstep.build import ensure_importable  # noqa: E402
+ensure_importable()
 
 
 def cases_of(fn):
@@ -35,6 +37,14 @@ def cases_of(fn):
             merged.update(part)
         out.append(merged)
     return out or [{}]
+
+
+def clear_sticky_error():
+    from soliton._C import lib
+    try:
+        lib.slb_clear_error()
+    except AttributeError:   # another build of libsoliton.so
+        pass
 
 
 def skipped_by_module(mod):
@@ -64,6 +74,7 @@ def run(modules):
                     passed.append(label)
                 except BaseException as e:   # a failing assert must not hide the tests after it
                     failed.append({"test": label, "error": "".join(traceback.format_exception_only(type(e), e)).strip()[-400:]})
+                    clear_sticky_error()     # nor may the library's sticky error code fail them in its wake
     return {"passed": len(passed), "failed": failed, "left_out_cpu_device": len(left_out), "skipped_modules": skipped,
             "passed_tests": passed}
 

@@ -11,7 +11,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libsoliton_b200.so")
 SOURCES = ["pool.cpp", "rendezvous.cpp", "dp_kernels.cu", "dp_engine.cu", "api.cu", "fabric_probe.cu"]
-HEADERS = ["pool.hpp", "rendezvous.hpp", "dp_types.h", "dp_launch.h", "dp_engine.hpp",
+HEADERS = ["pool.hpp", "rendezvous.hpp", "dp_types.h", "dp_launch.h", "dp_engine.hpp", "foreign_path.h",
            os.path.join("..", "..", "include", "soliton_b200.h")]
 NVCC_FLAGS = ["-std=c++17", "-O3", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
               "-Xcompiler", "-fPIC", "-shared"]

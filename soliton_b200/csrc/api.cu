@@ -10,11 +10,15 @@
 
 #include "../../include/soliton_b200.h"
 #include "dp_engine.hpp"
+#include "foreign_path.h"
 #include "pool.hpp"
 
 using namespace slb;
 
 static Engine& E() { return Engine::get(); }
+static inline const SlbForeignPath* foreign(int dev) {
+    return dev == DEV_CUDA && slb_foreign_path ? slb_foreign_path() : nullptr;
+}
 static inline void before_memory_op(int dev) {
     if (dev == DEV_CUDA) E().flush();  // nothing pending may outlive memory it points into
 }
@@ -123,32 +127,51 @@ void sl_fill(int dev, float* p, int64_t n, float v) {
 
 void sl_adamw(int dev, float* p, const float* g, float* m, float* v, int64_t n, float lr, float b1, float b2,
               float eps, float wd, int step) {
+    if (const SlbForeignPath* f = foreign(dev)) return f->adamw(p, g, m, v, n, lr, b1, b2, eps, wd, step);
     if (dev == DEV_CUDA)
         E().adamw(p, g, m, v, n, lr, b1, b2, eps, wd, step);
     else if (dev == DEV_CPU)
         E().set_error(ERR_NO_CPU_COMPUTE);
 }
-int sl_dist_unique_id(char* out128) { return E().dist_unique_id(out128); }
-int sl_dist_init(int rank, int world, const char* id128) { return E().dist_init(rank, world, id128); }
-int sl_dist_group(int dev, int start) { return dev == DEV_CUDA ? E().group(start) : 0; }
-int sl_dist_allreduce_mean(int dev, float* p, int64_t n) { return dev == DEV_CUDA ? E().allreduce_mean(p, n) : 0; }
-void sl_dist_destroy(void) { E().dist_destroy(); }
+int sl_dist_unique_id(char* out128) {
+    if (const SlbForeignPath* f = foreign(DEV_CUDA)) return f->dist_unique_id(out128);
+    return E().dist_unique_id(out128);
+}
+int sl_dist_init(int rank, int world, const char* id128) {
+    if (const SlbForeignPath* f = foreign(DEV_CUDA)) return f->dist_init(rank, world, id128);
+    return E().dist_init(rank, world, id128);
+}
+int sl_dist_group(int dev, int start) {
+    if (const SlbForeignPath* f = foreign(dev)) return f->dist_group(start);
+    return dev == DEV_CUDA ? E().group(start) : 0;
+}
+int sl_dist_allreduce_mean(int dev, float* p, int64_t n) {
+    if (const SlbForeignPath* f = foreign(dev)) return f->dist_allreduce_mean(p, n);
+    return dev == DEV_CUDA ? E().allreduce_mean(p, n) : 0;
+}
+void sl_dist_destroy(void) {
+    if (const SlbForeignPath* f = foreign(DEV_CUDA)) return f->dist_destroy();
+    E().dist_destroy();
+}
 
 // ---- next to the path
 
 void sl_axpy(int dev, const float* x, float* y, int64_t n, float alpha) {
+    if (const SlbForeignPath* f = foreign(dev)) return f->axpy(x, y, n, alpha);
     if (dev == DEV_CUDA)
         E().axpy(x, y, n, alpha);
     else if (dev == DEV_CPU)
         E().set_error(ERR_NO_CPU_COMPUTE);
 }
 void sl_scale(int dev, const float* x, float* y, int64_t n, float alpha) {
+    if (const SlbForeignPath* f = foreign(dev)) return f->scale(x, y, n, alpha);
     if (dev == DEV_CUDA)
         E().scale(x, y, n, alpha);
     else if (dev == DEV_CPU)
         E().set_error(ERR_NO_CPU_COMPUTE);
 }
 double sl_sumsq(int dev, const float* x, int64_t n) {
+    if (const SlbForeignPath* f = foreign(dev)) return f->sumsq(x, n);
     if (dev == DEV_CUDA) return E().sumsq(x, n);
     if (dev == DEV_CPU) E().set_error(ERR_NO_CPU_COMPUTE);
     return NAN;

@@ -599,8 +599,8 @@ __device__ __forceinline__ void gather_run(const LaunchArgs& a, const RankCtx& c
 // AHEAD_SMEM. The peer loads of both halves go through a ring of tile-sized stages in shared memory, filled by
 // asynchronous copies (cp.async, 16 bytes each, L2-only so no stale L1 line can serve them) that cost no registers
 // while they are in flight: kRingStages tiles of one peer stream in the gather half, kRingStages / (W - 1) tiles of
-// all W - 1 peer streams in the reduce half. A thread copies, waits for and reads back only its own 32 bytes of
-// each stage, so the ring needs no block-wide synchronisation. Ragged tiles and unaligned tensors bypass the ring.
+// all W - 1 peer streams in the reduce half. A warp copies, waits for and reads back only its own KiB of each
+// stage, so the ring needs no block-wide synchronisation. Ragged tiles and unaligned tensors bypass the ring.
 __device__ __forceinline__ void cp_async16(float* smem_dst, const float* gsrc) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(smem_dst)), "l"(gsrc)
                  : "memory");
@@ -616,6 +616,13 @@ __device__ __forceinline__ float8 ld_smem8(const float* p) {
     v.hi = reinterpret_cast<const float4*>(p)[1];
     return v;
 }
+// A warp owns 1 KiB of every tile stream (32 lanes x 8 floats). It fetches that KiB with two copy instructions of
+// 512 contiguous bytes each -- lane l moves 16 bytes at 16 l, then at 512 + 16 l -- so that every instruction fills
+// whole 32-byte sectors; a lane then reads ITS 32 bytes (at 32 l), which two other lanes of the warp brought in.
+// Hence the __syncwarp() on both sides of the read: after the copies have landed, and before the stage is refilled.
+__device__ __forceinline__ int warp_chunk(int half) {  // float offset inside a tile of this lane's 16 bytes
+    return (threadIdx.x >> 5) * 256 + half * 128 + (threadIdx.x & 31) * 4;
+}
 template <int W>
 constexpr int kStagedReduceAhead = kRingStages / (W - 1) > 0 ? kRingStages / (W - 1) : 1;
 // From six ranks on the reduce half keeps its loads in registers, all W of a tile at once: that already is five or
@@ -628,12 +635,13 @@ template <int W>
 __device__ __forceinline__ void stage_reduce(Ahead& ah, float* slot, const RankCtx& c, const int* prefix, int t, int t1,
                                              int me, int e) {
     if (t < t1 && ahead_seek(ah, c, prefix, t, me)) {
-        const int64_t off = (int64_t)(t - ah.first) * kTile + e;
+        const int64_t tile0 = (int64_t)(t - ah.first) * kTile;
+        const int lo = warp_chunk(0), hi = warp_chunk(1);
 #pragma unroll
         for (int k = 0; k < W - 1; k++) {
-            const float* g = peer_grad(ah.sg, k + (k >= me ? 1 : 0)) + off;
-            cp_async16(slot + k * kTile + e, g);
-            cp_async16(slot + k * kTile + e + 4, g + 4);
+            const float* g = peer_grad(ah.sg, k + (k >= me ? 1 : 0)) + tile0;
+            cp_async16(slot + k * kTile + lo, g + lo);
+            cp_async16(slot + k * kTile + hi, g + hi);
         }
     }
     cp_async_commit();
@@ -675,9 +683,11 @@ __device__ __forceinline__ void reduce_run_staged(const LaunchArgs& a, const Ran
                 vv = ld_stream8(s.v + off);
             }
             cp_async_wait<D - 1>();  // tile t's group is the oldest of the D outstanding
+            __syncwarp();
             float8 peer[W - 1];
 #pragma unroll
             for (int k = 0; k < W - 1; k++) peer[k] = ld_smem8(slot + k * kTile + e);
+            __syncwarp();
             stage_reduce<W>(ah, slot, c, prefix, t + D, t1, me, e);  // the stage is free: tile t + D goes into it
             const float8 avg = mul8(RankSum<W, W - 1>::upto(me, own, peer), a.inv_world);
             st_stream8(s.gme + off, avg);
@@ -702,9 +712,10 @@ __device__ __forceinline__ void reduce_run_staged(const LaunchArgs& a, const Ran
 __device__ __forceinline__ void stage_gather(Ahead& ah, float* slot, const RankCtx& c, const int* prefix, int t, int t1,
                                              int src, int e) {
     if (t < t1 && ahead_seek(ah, c, prefix, t, src)) {
-        const float* g = ah.gsrc + (int64_t)(t - ah.first) * kTile + e;
-        cp_async16(slot + e, g);
-        cp_async16(slot + e + 4, g + 4);
+        const float* g = ah.gsrc + (int64_t)(t - ah.first) * kTile;
+        const int lo = warp_chunk(0), hi = warp_chunk(1);
+        cp_async16(slot + lo, g + lo);
+        cp_async16(slot + hi, g + hi);
     }
     cp_async_commit();
 }
@@ -736,7 +747,9 @@ __device__ __forceinline__ void gather_run_staged(const LaunchArgs& a, const Ran
                 vv = ld_stream8(s.v + off);
             }
             cp_async_wait<D - 1>();
+            __syncwarp();
             const float8 avg = ld_smem8(slot + e);
+            __syncwarp();
             stage_gather(ah, slot, c, prefix, t + D, t1, src, e);
             st_stream8(s.gme + off, avg);
             if (adam) {

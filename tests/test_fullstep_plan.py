@@ -40,6 +40,7 @@ def plans(built):
     sys.path.insert(0, ROOT)
     from fullstep import build as fb
     fb.build()
+    fb.ensure_importable()
     if not os.path.exists(os.path.join(REF, "soliton", "__init__.pyc")):
         pytest.skip("the reference's Python package is not compiled (no reference checkout at build time)")
     r = subprocess.run([sys.executable, "-c", SCRIPT, REF], capture_output=True, text=True, timeout=600)

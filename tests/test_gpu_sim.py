@@ -43,7 +43,7 @@ def large_kernel(request):
     """Runs a test once with each way the two-shot kernel can run its peer loads ahead of the arithmetic."""
     set_option("prefetch", request.param)
     yield request.param
-    set_option("prefetch", 2)
+    set_option("prefetch", 0)
 
 
 @pytest.mark.parametrize("mode", [1, 2], ids=["oneshot", "twoshot"])
