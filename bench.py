@@ -67,7 +67,6 @@ def parse():
     ap.add_argument("--mode", type=int, default=0, help="0 auto, 1 one-shot, 2 two-shot")
     ap.add_argument("--blocks-per-sm", type=int, default=0)
     ap.add_argument("--cyclic", type=int, default=-1)
-    ap.add_argument("--prefetch", type=int, default=-1, help="two-shot peer loads: 0 on demand, 1 register ring, 2 shared-memory ring")
     ap.add_argument("--stamps", action="store_true", help="device times at the phase borders of the last launch")
     ap.add_argument("--sweep", action="store_true", help="bucket-size sweep 4 KB .. 1 GB, one-shot vs two-shot (N >= 2)")
     ap.add_argument("--fabric", action="store_true", help="NVLink fabric ceiling: copy engines and kernels, one and both directions")
@@ -418,9 +417,8 @@ def run_ours(args, rank, local_rank, world):
     for name, value in (("mode", args.mode), ("blocks_per_sm", args.blocks_per_sm)):
         if value:
             set_option(name, value)
-    for name, value in (("cyclic", args.cyclic), ("prefetch", args.prefetch)):
-        if value >= 0:
-            set_option(name, value)
+    if args.cyclic >= 0:
+        set_option("cyclic", args.cyclic)
     if args.stamps:
         set_option("stamps", 1)
 
@@ -513,7 +511,9 @@ def run_ours(args, rank, local_rank, world):
                       "us_total_block0": (t[4] - t[0]) / 1e3}
 
     # host-fed step: gradients up, parameters down, bucket by bucket over the copy streams
-    opt.bind_host(pinned_g, pinned_out)
+    # gradients differ per rank: every rank uploads its own; parameters come out identical on all ranks: each rank
+    # reads back its 1 / world share, so that the job has them on the host once
+    opt.bind_host(pinned_g, pinned_out, share=(rank, world))
     e2e_ms, breakdown = None, None
     if not args.bare:
         opt.host_step()
@@ -576,7 +576,8 @@ def run_ours(args, rank, local_rank, world):
                    "exchange": {0: "none", 1: "one-shot", 2: "two-shot"}[mode], "blocks_per_rank": blocks,
                    "optimizer": "none (--bare)" if args.bare else "AdamW",
                    "arithmetic": "gradient mean, m, v in f32; parameter update in f64, rounded to f32 once",
-                   "e2e_copies": "h2d: this step's gradients from pinned memory; d2h: updated parameters; "
+                   "e2e_copies": "h2d: this rank's gradients from pinned memory; d2h: updated parameters, each rank its "
+                                 "1/world share (all ranks hold the same bits, checked in `parity`); "
                                  f"buckets of {args.bucket_mb} MiB over two copy streams beside the kernels"},
         "regions": {"n": len(region_ms), "steps_each": args.steps, "ms_per_step_median": ms,
                     "ms_per_step_min": min(region_ms), "ms_per_step_max": max(region_ms)},
@@ -585,7 +586,9 @@ def run_ours(args, rank, local_rank, world):
     }
     if e2e_ms is not None:
         line["e2e"] = {"value": world * BYTES_PER_PARAM * P / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
-                       "h2d_bytes_per_step": 4 * P, "d2h_bytes_per_step": 4 * P, "ms_per_step": e2e_ms,
+                       "h2d_bytes_per_step": opt.upload_bytes, "d2h_bytes_per_step": opt.download_bytes,
+                       "bytes_are": "per rank; the job moves world x h2d up and, over all ranks together, every parameter down once",
+                       "ms_per_step": e2e_ms,
                        "steps": args.e2e_steps, "breakdown": breakdown}
     if stamps:
         line["phases_block0_last_launch"] = stamps

@@ -131,8 +131,7 @@ int sl_cuda_dp_set_workspace(void* p, size_t n);
 size_t slb_workspace_bytes(void);
 /* Options: "eager" (0/1: launch at every call instead of deferring -- with it a Soliton build needs no slb_flush
  * hooks at all), "mode" (0 auto, 1 one-shot, 2 two-shot), "blocks_per_sm", "cyclic" (single-rank steps: blocks take
- * groups of this many tiles round robin; 0 = one contiguous run per block; default 4), "prefetch" (two-shot: peer
- * loads run a few tiles ahead of the arithmetic; default 1; same bits either way), "stamps" (collective launches
+ * groups of this many tiles round robin; 0 = one contiguous run per block; default 4), "stamps" (collective launches
  * record device times at their phase borders, see slb_read_stamps), "overlap" (1: the path's launches go to a stream
  * of their own beside the legacy stream, ordered against it by events; default 0), "timeout_ms" (device waits),
  * "host_timeout_ms", "oneshot_max_bytes" (-1: whatever fits the staging slots). Must be set alike on all ranks.

@@ -39,9 +39,9 @@ class _Copies:
     def __init__(self, device_ptrs, host_ptrs, nbytes):
         k = len(device_ptrs)
         self.k = k
-        self.dev = (ctypes.c_void_p * k)(*device_ptrs)
-        self.host = (ctypes.c_void_p * k)(*host_ptrs)
-        self.bytes = (ctypes.c_size_t * k)(*nbytes)
+        self.dev = (ctypes.c_void_p * max(k, 1))(*device_ptrs)
+        self.host = (ctypes.c_void_p * max(k, 1))(*host_ptrs)
+        self.bytes = (ctypes.c_size_t * max(k, 1))(*nbytes)
 
 
 class BucketedAdamW(AdamW):
@@ -77,16 +77,36 @@ class BucketedAdamW(AdamW):
 
     # --- host-fed steps
 
-    def bind_host(self, host_grads, host_params):
+    def bind_host(self, host_grads, host_params, share=None):
         """Pinned host buffers, one per parameter (objects with data_ptr(), or addresses): where gradients come from
-        and where updated parameters go. Gradient tensors must already hang on the parameters."""
+        and where updated parameters go. Gradient tensors must already hang on the parameters.
+
+        `share` = (rank, world): after a data-parallel step every rank holds the same parameter bits, so the job
+        needs them on the host once, not once per rank. Rank r then reads back only its share -- elements
+        [n r / world, n (r + 1) / world) of every tensor of 64 KiB or more, and the whole of every world-th small
+        tensor -- into the same places of its host buffers; the rest of those buffers is not written."""
         addr = lambda x: x.data_ptr() if hasattr(x, "data_ptr") else int(x)  # noqa: E731
+        rank, world = share if share else (0, 1)
         self._up, self._down = [], []
+        self.upload_bytes = self.download_bytes = 0
         for bucket in self.buckets:
             ps = [self._slots[i].param for i in bucket]
             nb = [4 * p.numel for p in ps]
             self._up.append(_Copies([p.grad.ptr for p in ps], [addr(host_grads[i]) for i in bucket], nb))
-            self._down.append(_Copies([p.ptr for p in ps], [addr(host_params[i]) for i in bucket], nb))
+            self.upload_bytes += sum(nb)
+            dev, host, size = [], [], []
+            for i, p in zip(bucket, ps):
+                n = p.numel
+                if 4 * n >= (64 << 10):
+                    lo, hi = n * rank // world, n * (rank + 1) // world
+                elif i % world == rank:
+                    lo, hi = 0, n
+                else:
+                    continue
+                if hi > lo:
+                    dev.append(p.ptr + 4 * lo), host.append(addr(host_params[i]) + 4 * lo), size.append(4 * (hi - lo))
+            self._down.append(_Copies(dev, host, size))
+            self.download_bytes += sum(size)
 
     def upload(self, b):
         c = self._up[b]
@@ -95,7 +115,7 @@ class BucketedAdamW(AdamW):
 
     def download(self, b):
         c = self._down[b]
-        if lib.slb_to_host_async(c.k, c.host, c.dev, c.bytes) != 0:
+        if c.k and lib.slb_to_host_async(c.k, c.host, c.dev, c.bytes) != 0:
             raise RuntimeError("soliton: asynchronous download failed")
 
     def host_step(self):

@@ -200,7 +200,6 @@ int slb_set_option(const char* name, int64_t value) {
     if (!strcmp(name, "eager")) o.eager = (int)value;
     else if (!strcmp(name, "mode")) o.mode = (int)value;
     else if (!strcmp(name, "blocks_per_sm")) o.blocks_per_sm = (int)value;
-    else if (!strcmp(name, "prefetch")) o.prefetch = (int)value;
     else if (!strcmp(name, "stamps")) o.stamps = (int)value;
     else if (!strcmp(name, "overlap")) {
         if (E().cuda_ready()) E().sync();  // launches change stream: nothing may be in flight across the switch

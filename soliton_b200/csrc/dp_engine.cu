@@ -534,15 +534,14 @@ int Engine::launch_items(std::vector<StepItem>& items, const std::vector<HyperKe
         oneshot = fits && (opt.mode == 1 || (opt.mode == 0 && small));
     }
     const int kind = oneshot ? KERNEL_ONESHOT : KERNEL_PLAIN;
-    const int deep = W > 1 && !oneshot ? opt.prefetch : AHEAD_NONE;
-    const size_t smem = step_smem(W, kind, deep, nseg);
+    const size_t smem = (size_t)(nseg + 1) * sizeof(int);
     int per_sm;
     if (W > 1) {
         per_sm = kCollectiveBlocksPerSm;
         if (opt.blocks_per_sm > 0 && opt.blocks_per_sm < per_sm) per_sm = opt.blocks_per_sm;
-        if (step_occupancy(W, adam, kind, deep, smem) < per_sm) return ERR_LAUNCH;
+        if (step_occupancy(W, adam, kind, smem) < per_sm) return ERR_LAUNCH;
     } else {
-        per_sm = step_occupancy(W, adam, kind, deep, smem);
+        per_sm = step_occupancy(W, adam, kind, smem);
         if (opt.blocks_per_sm > 0 && opt.blocks_per_sm < per_sm) per_sm = opt.blocks_per_sm;
         if (per_sm < 1) return ERR_LAUNCH;
     }
@@ -595,7 +594,7 @@ int Engine::launch_items(std::vector<StepItem>& items, const std::vector<HyperKe
     last_mode = W == 1 ? 0 : (oneshot ? 1 : 2);
     last_blocks = G;
     launches++;
-    const int rc = launch_step(W, adam, kind, deep, false, G, smem, a, st);
+    const int rc = launch_step(W, adam, kind, false, G, smem, a, st);
     if (tracked && lanes_.end(Lanes::STEP, st) != 0) return ERR_LAUNCH;
     if (W > 1) fused_.valid = false;  // any collective launch reuses the staging area
     if (rc == 0 && a.sumsq_on) {
@@ -1172,9 +1171,8 @@ int Engine::sim_step(int world, int nseg, const int64_t* n, float* const* p, flo
     bool oneshot = world > 1 && fits && (mode == 1 || (mode == 0 && T * kTile * 4 <= (opt.oneshot_max_bytes < 0 ? INT64_MAX : opt.oneshot_max_bytes)));
     if (mode == 1 && !oneshot) return -4;  // asked for one-shot, but the step does not fit the staging slots
     const int kind = oneshot ? KERNEL_ONESHOT : KERNEL_PLAIN;
-    const int deep = world > 1 && !oneshot ? opt.prefetch : AHEAD_NONE;
-    const size_t smem = step_smem(world, kind, deep, nseg);
-    const int occ = step_occupancy(world, adam != 0, kind, deep, smem);
+    const size_t smem = (size_t)(nseg + 1) * sizeof(int);
+    const int occ = step_occupancy(world, adam != 0, kind, smem);
     const int cap = occ * sm_count_ / (int)ctxs.size();
     if (cap < 1) return -3;
     const int work = (world == 1 || oneshot) ? (int)T : min_chunk((int)T, world);
@@ -1195,7 +1193,7 @@ int Engine::sim_step(int world, int nseg, const int64_t* n, float* const* p, flo
     last_mode = world == 1 ? 0 : (oneshot ? 1 : 2);
     last_blocks = G;
     launches++;
-    if (launch_step(world, adam != 0, kind, deep, true, G * (int)ctxs.size(), smem, a, 0) != 0) {
+    if (launch_step(world, adam != 0, kind, true, G * (int)ctxs.size(), smem, a, 0) != 0) {
         cudaGetLastError();
         return -5;
     }

@@ -38,8 +38,6 @@ struct Options {
     int blocks_per_sm = 0;                  // 0: as many as are resident
     int cyclic = 4;                         // single-rank step: blocks take groups of this many tiles round robin, so
                                             // that resident blocks walk each tensor side by side; 0: one contiguous run
-    int prefetch = 0;                       // two-shot: how peer loads run ahead of the arithmetic: 0 not at all, 1 a short
-                                            // register ring, 2 a shared-memory ring filled by cp.async (same bits whichever)
     int stamps = 0;                         // collective launches record device times at their phase borders
     int overlap = 0;                        // 1: path launches go to a stream of their own instead of the legacy stream
     unsigned long long timeout_ns = 10ull * 1000 * 1000 * 1000;  // bound of every device-side flag wait

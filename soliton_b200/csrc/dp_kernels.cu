@@ -9,18 +9,17 @@
 // number of blocks that are resident at once. Peer gradients are read and written directly through
 // NVSwitch-mapped pointers; no library collective runs.
 //
-//   k_twoshot<W,ADAM,AHEAD>  reduce-scatter + all-gather. Rank c owns chunk c of the tile sequence: it pulls that
-//                      chunk from every rank, sums in rank order 0..W-1, multiplies by 1/W, stores the mean into its
-//                      own gradient and (ADAM) updates its own p, m, v on the spot. Then it pulls every other chunk's
+//   k_twoshot<W,ADAM>  reduce-scatter + all-gather. Rank c owns chunk c of the tile sequence: it pulls that chunk
+//                      from every rank, sums in rank order 0..W-1, multiplies by 1/W, stores the mean into its own
+//                      gradient and (ADAM) updates its own p, m, v on the spot. Then it pulls every other chunk's
 //                      mean from its owner, stores it into its local gradient and updates p, m, v there.
 //                      With W == 1 this is the plain multi-tensor AdamW step.
-//                      AHEAD: loads that cross NVLink run a few tiles ahead of the arithmetic. A peer load takes
-//                      several microseconds under load, and with one 32-byte load per thread outstanding an SM holds
-//                      16 KiB in flight, which caps the link near 600 GB/s. AHEAD_SMEM stages the peers' tiles in a
-//                      shared-memory ring filled by cp.async (no registers held while in flight, 56 KiB per block);
-//                      AHEAD_REGS keeps a short ring in registers; AHEAD_NONE issues a tile's loads when it needs them.
 //                      Without an optimizer (ADAM = false) the owner also accumulates the sum of squares of the
 //                      mean it produces, piece by piece, for the gradient clip that follows such a launch.
+//                      A tile's loads are all issued when the tile is reached. Running the peer loads several tiles
+//                      ahead (a register ring; a shared-memory ring filled by cp.async) was built and measured on
+//                      2, 4 and 8 GPUs: no faster at best, so it is not here. The fabric, not the depth of
+//                      outstanding loads, bounds the exchange.
 //   k_oneshot<W,ADAM>  for small steps: every rank pushes its gradients into a staging slot on every peer, one
 //                      barrier, then every rank reduces all W copies locally in the same rank order.
 //
@@ -188,12 +187,6 @@ __device__ __forceinline__ float8 add8(const float8& a, const float8& b) {
 __device__ __forceinline__ float8 mul8(const float8& a, float s) {
     float8 r;
     r.lo = mul4(a.lo, s), r.hi = mul4(a.hi, s);
-    return r;
-}
-__device__ __forceinline__ float8 sel8(bool c, const float8& a, const float8& b) {
-    float8 r;
-    r.lo = make_float4(c ? a.lo.x : b.lo.x, c ? a.lo.y : b.lo.y, c ? a.lo.z : b.lo.z, c ? a.lo.w : b.lo.w);
-    r.hi = make_float4(c ? a.hi.x : b.hi.x, c ? a.hi.y : b.hi.y, c ? a.hi.z : b.hi.z, c ? a.hi.w : b.hi.w);
     return r;
 }
 // acc += x^2 over the eight floats of v, in element order, in double (one FMA each).
@@ -379,33 +372,7 @@ __device__ __forceinline__ void do_run(const LaunchArgs& a, const RankCtx& c, co
     }
 }
 
-// ---------------------------------------------------------------- the two halves of two-shot, peer loads running ahead
-
-// AHEAD_REGS. How many tiles the peer loads of the reduce half run ahead of the arithmetic, held in a register ring:
-// W - 1 peer streams per tile. 0: all W loads of a tile are issued together and nothing runs ahead (from four ranks
-// on a single tile already has three or more peer loads per thread outstanding).
-template <int W, bool ADAM>
-constexpr int kReduceAhead = W == 2 ? 2 : (W == 3 ? 1 : 0);
-// Tiles the single peer stream of the gather half runs ahead. More than these, and the optimizer variants spill.
-template <bool ADAM>
-constexpr int kGatherAhead = ADAM ? 2 : 4;
-
-// Where the loads that run ahead currently are: the segment of the tile they fetch.
-struct Ahead {
-    const Seg* sg;
-    float* gsrc;
-    int64_t n;
-    int vec, first, end;
-};
-__device__ __forceinline__ bool ahead_seek(Ahead& ah, const RankCtx& c, const int* prefix, int t, int src) {
-    if (t >= ah.end || t < ah.first) {
-        const int i = find_seg(prefix, c.nseg, t);
-        ah.sg = c.segs + i;
-        ah.gsrc = peer_grad(ah.sg, src);
-        ah.n = ah.sg->n, ah.vec = ah.sg->vec, ah.first = prefix[i], ah.end = prefix[i + 1];
-    }
-    return ah.vec && ah.n - (int64_t)(t - ah.first) * kTile >= kTile;  // a whole, aligned tile: the 256-bit path
-}
+// ---------------------------------------------------------------- the two halves of two-shot
 
 // The sum of squares of the mean a block produced since `first`: per thread in element order, then a fixed tree.
 struct Piece {
@@ -432,340 +399,26 @@ __device__ __forceinline__ void flush_piece(const RankCtx& c, Piece& pc, double*
     pc.acc = 0;
 }
 
-// Value of rank R in the rank-ordered sum: this rank's own gradient at position `me`, the peers' (held without the
-// own one, in rank order) around it. `me` is not a compile-time constant, hence the selects.
-template <int W, int R>
-__device__ __forceinline__ float8 rank_value(int me, const float8& own, const float8 (&peer)[W - 1]) {
-    if constexpr (R == 0)
-        return sel8(me == 0, own, peer[0]);
-    else if constexpr (R == W - 1)
-        return sel8(me == W - 1, own, peer[W - 2]);
-    else
-        return sel8(R == me, own, sel8(R < me, peer[R], peer[R - 1]));
-}
-// ((x0 + x1) + x2) + ... + xR
-template <int W, int R>
-struct RankSum {
-    static __device__ __forceinline__ float8 upto(int me, const float8& own, const float8 (&peer)[W - 1]) {
-        return add8(RankSum<W, R - 1>::upto(me, own, peer), rank_value<W, R>(me, own, peer));
-    }
-};
-template <int W>
-struct RankSum<W, 0> {
-    static __device__ __forceinline__ float8 upto(int me, const float8& own, const float8 (&peer)[W - 1]) {
-        return rank_value<W, 0>(me, own, peer);
-    }
-};
-
-template <int W>
-__device__ __forceinline__ void ahead_reduce(Ahead& ah, float8 (&slot)[W - 1], const RankCtx& c, const int* prefix, int t,
-                                             int t1, int me, int e) {
-    if (t >= t1) return;
-    if (!ahead_seek(ah, c, prefix, t, me)) return;
-    const int64_t off = (int64_t)(t - ah.first) * kTile + e;
-#pragma unroll
-    for (int k = 0; k < W - 1; k++) slot[k] = ld_sys8(peer_grad(ah.sg, k + (k >= me ? 1 : 0)) + off);
-}
-
 // Reduce half: the run [t0, t1) of this rank's own chunk. Mean in rank order, stored into the own gradient, and
-// the update of the own p, m, v (ADAM) or the sum of squares of the mean (no optimizer) on the spot.
-template <int W, bool ADAM, int AHEAD>
+// the update of the own p, m, v (ADAM) or the sum of squares of the mean (no optimizer) on the spot. A piece of
+// the sum of squares ends where the segment changes and where the run ends.
+template <int W, bool ADAM>
 __device__ __forceinline__ void reduce_run(const LaunchArgs& a, const RankCtx& c, const int* prefix, int t0, int t1, int me,
                                            double* s_red) {
-    constexpr int D = AHEAD == AHEAD_REGS ? kReduceAhead<W, ADAM> : 0;
-    constexpr int RD = D > 0 ? D : 1;
-    constexpr bool SUMSQ = !ADAM;
-    const bool pieces = SUMSQ && a.sumsq_on;
-    float8 ring[RD][W - 1];  // D > 0: the peers' values of tiles t .. t + D - 1
+    const bool pieces = !ADAM && a.sumsq_on;
     SegView s;
     s.first_tile = 0, s.end_tile = 0;
-    Ahead ah;
-    ah.first = 0, ah.end = 0;
     Piece pc;
     pc.acc = 0, pc.first = t0;
-    const int e = threadIdx.x * 8;
-    if (D > 0) {
-#pragma unroll
-        for (int j = 0; j < RD; j++) ahead_reduce<W>(ah, ring[j], c, prefix, t0 + j, t1, me, e);
-    }
-    for (int tb = t0; tb < t1; tb += RD) {
-#pragma unroll
-        for (int j = 0; j < RD; j++) {
-            const int t = tb + j;
-            if (t >= t1) break;
-            if (t >= s.end_tile || t < s.first_tile) {
-                if (pieces && t > pc.first) flush_piece<W>(c, pc, s_red);
-                load_seg(s, c, prefix, t, me, me);
-                pc.first = t;
-            }
-            const int64_t base = (int64_t)(t - s.first_tile) * kTile;
-            if (D > 0 && s.vec && s.n - base >= kTile) {
-                const int64_t off = base + e;
-                const bool adam = ADAM && s.p != nullptr;
-                const float8 own = ld_sys8(s.gme + off);
-                float8 pv, mv, vv;
-                if (adam) {
-                    pv = ld_stream8(s.p + off);
-                    mv = ld_stream8(s.m + off);
-                    vv = ld_stream8(s.v + off);
-                }
-                float8 peer[W - 1];
-#pragma unroll
-                for (int k = 0; k < W - 1; k++) peer[k] = ring[j][k];
-                ahead_reduce<W>(ah, ring[j], c, prefix, t + D, t1, me, e);  // the slot is free: fetch tile t + D into it
-                const float8 avg = mul8(RankSum<W, W - 1>::upto(me, own, peer), a.inv_world);
-                st_stream8(s.gme + off, avg);
-                if (SUMSQ) pc.acc = sumsq8(pc.acc, avg);
-                if (adam) {
-                    const Hyper& h = a.hp[s.hyper];
-                    adamw_vec(pv.lo, avg.lo, mv.lo, vv.lo, h, s.wd);
-                    adamw_vec(pv.hi, avg.hi, mv.hi, vv.hi, h, s.wd);
-                    st_stream8(s.p + off, pv);
-                    st_stream8(s.m + off, mv);
-                    st_stream8(s.v + off, vv);
-                }
-            } else {
-                if (D > 0) ahead_reduce<W>(ah, ring[j], c, prefix, t + D, t1, me, e);
-                do_tile<W, ADAM, REDUCE_OWN>(s, a, c, t, me, nullptr, 0, pc.acc);
-            }
-        }
-    }
-    if (pieces && t1 > pc.first) flush_piece<W>(c, pc, s_red);
-}
-
-__device__ __forceinline__ void ahead_gather(Ahead& ah, float8& slot, const RankCtx& c, const int* prefix, int t, int t1,
-                                             int src, int e) {
-    if (t >= t1) return;
-    if (!ahead_seek(ah, c, prefix, t, src)) return;
-    slot = ld_sys8(ah.gsrc + (int64_t)(t - ah.first) * kTile + e);
-}
-
-// Gather half: the run [t0, t1) of chunk `src`, whose mean its owner has published. Copies the mean into the local
-// gradient and updates the local p, m, v with it.
-template <int W, bool ADAM, int AHEAD>
-__device__ __forceinline__ void gather_run(const LaunchArgs& a, const RankCtx& c, const int* prefix, int t0, int t1, int me,
-                                           int src) {
-    constexpr int D = AHEAD == AHEAD_REGS ? kGatherAhead<ADAM> : 0;
-    constexpr int RD = D > 0 ? D : 1;
-    float8 ring[RD];  // D > 0: the owner's values of tiles t .. t + D - 1
-    SegView s;
-    s.first_tile = 0, s.end_tile = 0;
-    Ahead ah;
-    ah.first = 0, ah.end = 0;
-    double unused = 0;
-    const int e = threadIdx.x * 8;
-    if (D > 0) {
-#pragma unroll
-        for (int j = 0; j < RD; j++) ahead_gather(ah, ring[j], c, prefix, t0 + j, t1, src, e);
-    }
-    for (int tb = t0; tb < t1; tb += RD) {
-#pragma unroll
-        for (int j = 0; j < RD; j++) {
-            const int t = tb + j;
-            if (t >= t1) break;
-            if (t >= s.end_tile || t < s.first_tile) load_seg(s, c, prefix, t, me, src);
-            const int64_t base = (int64_t)(t - s.first_tile) * kTile;
-            if (D > 0 && s.vec && s.n - base >= kTile) {
-                const int64_t off = base + e;
-                const bool adam = ADAM && s.p != nullptr;
-                float8 pv, mv, vv;
-                if (adam) {
-                    pv = ld_stream8(s.p + off);
-                    mv = ld_stream8(s.m + off);
-                    vv = ld_stream8(s.v + off);
-                }
-                const float8 avg = ring[j];
-                ahead_gather(ah, ring[j], c, prefix, t + D, t1, src, e);  // the slot is free: fetch tile t + D into it
-                st_stream8(s.gme + off, avg);
-                if (adam) {
-                    const Hyper& h = a.hp[s.hyper];
-                    adamw_vec(pv.lo, avg.lo, mv.lo, vv.lo, h, s.wd);
-                    adamw_vec(pv.hi, avg.hi, mv.hi, vv.hi, h, s.wd);
-                    st_stream8(s.p + off, pv);
-                    st_stream8(s.m + off, mv);
-                    st_stream8(s.v + off, vv);
-                }
-            } else {
-                if (D > 0) ahead_gather(ah, ring[j], c, prefix, t + D, t1, src, e);
-                do_tile<W, ADAM, GATHER>(s, a, c, t, me, nullptr, 0, unused);
-            }
-        }
-    }
-}
-
-
-// ---------------------------------------------------------------- the two halves of two-shot, peer tiles staged in shared memory
-
-// AHEAD_SMEM. The peer loads of both halves go through a ring of tile-sized stages in shared memory, filled by
-// asynchronous copies (cp.async, 16 bytes each, L2-only so no stale L1 line can serve them) that cost no registers
-// while they are in flight: kRingStages tiles of one peer stream in the gather half, kRingStages / (W - 1) tiles of
-// all W - 1 peer streams in the reduce half. A warp copies, waits for and reads back only its own KiB of each
-// stage, so the ring needs no block-wide synchronisation. Ragged tiles and unaligned tensors bypass the ring.
-__device__ __forceinline__ void cp_async16(float* smem_dst, const float* gsrc) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(smem_dst)), "l"(gsrc)
-                 : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {  // all but the N most recent groups of this thread have landed
-    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
-__device__ __forceinline__ float8 ld_smem8(const float* p) {
-    float8 v;
-    v.lo = reinterpret_cast<const float4*>(p)[0];
-    v.hi = reinterpret_cast<const float4*>(p)[1];
-    return v;
-}
-// A warp owns 1 KiB of every tile stream (32 lanes x 8 floats). It fetches that KiB with two copy instructions of
-// 512 contiguous bytes each -- lane l moves 16 bytes at 16 l, then at 512 + 16 l -- so that every instruction fills
-// whole 32-byte sectors; a lane then reads ITS 32 bytes (at 32 l), which two other lanes of the warp brought in.
-// Hence the __syncwarp() on both sides of the read: after the copies have landed, and before the stage is refilled.
-__device__ __forceinline__ int warp_chunk(int half) {  // float offset inside a tile of this lane's 16 bytes
-    return (threadIdx.x >> 5) * 256 + half * 128 + (threadIdx.x & 31) * 4;
-}
-template <int W>
-constexpr int kStagedReduceAhead = kRingStages / (W - 1) > 0 ? kRingStages / (W - 1) : 1;
-// From six ranks on the reduce half keeps its loads in registers, all W of a tile at once: that already is five or
-// more peer loads per thread in flight, and holding W - 1 staged tiles next to p, m, v would spill.
-constexpr int kStagedReduceMaxWorld = 5;
-
-// Starts the copies of tile t of the reduce half into stage `slot` (W - 1 peer streams) and closes the group;
-// the group is empty when t lies beyond the run or is not a whole aligned tile, so that groups stay one per tile.
-template <int W>
-__device__ __forceinline__ void stage_reduce(Ahead& ah, float* slot, const RankCtx& c, const int* prefix, int t, int t1,
-                                             int me, int e) {
-    if (t < t1 && ahead_seek(ah, c, prefix, t, me)) {
-        const int64_t tile0 = (int64_t)(t - ah.first) * kTile;
-        const int lo = warp_chunk(0), hi = warp_chunk(1);
-#pragma unroll
-        for (int k = 0; k < W - 1; k++) {
-            const float* g = peer_grad(ah.sg, k + (k >= me ? 1 : 0)) + tile0;
-            cp_async16(slot + k * kTile + lo, g + lo);
-            cp_async16(slot + k * kTile + hi, g + hi);
-        }
-    }
-    cp_async_commit();
-}
-
-template <int W, bool ADAM>
-__device__ __forceinline__ void reduce_run_staged(const LaunchArgs& a, const RankCtx& c, const int* prefix, float* ring,
-                                                  int t0, int t1, int me, double* s_red) {
-    constexpr int D = kStagedReduceAhead<W>;
-    constexpr int kStage = (W - 1) * kTile;  // floats per stage
-    constexpr bool SUMSQ = !ADAM;
-    const bool pieces = SUMSQ && a.sumsq_on;
-    SegView s;
-    s.first_tile = 0, s.end_tile = 0;
-    Ahead ah;
-    ah.first = 0, ah.end = 0;
-    Piece pc;
-    pc.acc = 0, pc.first = t0;
-    const int e = threadIdx.x * 8;
-    for (int j = 0; j < D; j++) stage_reduce<W>(ah, ring + j * kStage, c, prefix, t0 + j, t1, me, e);
-    int j = 0;
     for (int t = t0; t < t1; t++) {
-        float* slot = ring + j * kStage;
-        j = j + 1 == D ? 0 : j + 1;
         if (t >= s.end_tile || t < s.first_tile) {
             if (pieces && t > pc.first) flush_piece<W>(c, pc, s_red);
             load_seg(s, c, prefix, t, me, me);
             pc.first = t;
         }
-        const int64_t base = (int64_t)(t - s.first_tile) * kTile;
-        if (s.vec && s.n - base >= kTile) {
-            const int64_t off = base + e;
-            const bool adam = ADAM && s.p != nullptr;
-            const float8 own = ld_sys8(s.gme + off);
-            float8 pv, mv, vv;
-            if (adam) {
-                pv = ld_stream8(s.p + off);
-                mv = ld_stream8(s.m + off);
-                vv = ld_stream8(s.v + off);
-            }
-            cp_async_wait<D - 1>();  // tile t's group is the oldest of the D outstanding
-            __syncwarp();
-            float8 peer[W - 1];
-#pragma unroll
-            for (int k = 0; k < W - 1; k++) peer[k] = ld_smem8(slot + k * kTile + e);
-            __syncwarp();
-            stage_reduce<W>(ah, slot, c, prefix, t + D, t1, me, e);  // the stage is free: tile t + D goes into it
-            const float8 avg = mul8(RankSum<W, W - 1>::upto(me, own, peer), a.inv_world);
-            st_stream8(s.gme + off, avg);
-            if (SUMSQ) pc.acc = sumsq8(pc.acc, avg);
-            if (adam) {
-                const Hyper& h = a.hp[s.hyper];
-                adamw_vec(pv.lo, avg.lo, mv.lo, vv.lo, h, s.wd);
-                adamw_vec(pv.hi, avg.hi, mv.hi, vv.hi, h, s.wd);
-                st_stream8(s.p + off, pv);
-                st_stream8(s.m + off, mv);
-                st_stream8(s.v + off, vv);
-            }
-        } else {
-            stage_reduce<W>(ah, slot, c, prefix, t + D, t1, me, e);
-            do_tile<W, ADAM, REDUCE_OWN>(s, a, c, t, me, nullptr, 0, pc.acc);
-        }
+        do_tile<W, ADAM, REDUCE_OWN>(s, a, c, t, me, nullptr, 0, pc.acc);
     }
-    cp_async_wait<0>();
     if (pieces && t1 > pc.first) flush_piece<W>(c, pc, s_red);
-}
-
-__device__ __forceinline__ void stage_gather(Ahead& ah, float* slot, const RankCtx& c, const int* prefix, int t, int t1,
-                                             int src, int e) {
-    if (t < t1 && ahead_seek(ah, c, prefix, t, src)) {
-        const float* g = ah.gsrc + (int64_t)(t - ah.first) * kTile;
-        const int lo = warp_chunk(0), hi = warp_chunk(1);
-        cp_async16(slot + lo, g + lo);
-        cp_async16(slot + hi, g + hi);
-    }
-    cp_async_commit();
-}
-
-template <int W, bool ADAM>
-__device__ __forceinline__ void gather_run_staged(const LaunchArgs& a, const RankCtx& c, const int* prefix, float* ring,
-                                                  int t0, int t1, int me, int src) {
-    constexpr int D = kRingStages;
-    SegView s;
-    s.first_tile = 0, s.end_tile = 0;
-    Ahead ah;
-    ah.first = 0, ah.end = 0;
-    double unused = 0;
-    const int e = threadIdx.x * 8;
-    for (int j = 0; j < D; j++) stage_gather(ah, ring + j * kTile, c, prefix, t0 + j, t1, src, e);
-    int j = 0;
-    for (int t = t0; t < t1; t++) {
-        float* slot = ring + j * kTile;
-        j = j + 1 == D ? 0 : j + 1;
-        if (t >= s.end_tile || t < s.first_tile) load_seg(s, c, prefix, t, me, src);
-        const int64_t base = (int64_t)(t - s.first_tile) * kTile;
-        if (s.vec && s.n - base >= kTile) {
-            const int64_t off = base + e;
-            const bool adam = ADAM && s.p != nullptr;
-            float8 pv, mv, vv;
-            if (adam) {
-                pv = ld_stream8(s.p + off);
-                mv = ld_stream8(s.m + off);
-                vv = ld_stream8(s.v + off);
-            }
-            cp_async_wait<D - 1>();
-            __syncwarp();
-            const float8 avg = ld_smem8(slot + e);
-            __syncwarp();
-            stage_gather(ah, slot, c, prefix, t + D, t1, src, e);
-            st_stream8(s.gme + off, avg);
-            if (adam) {
-                const Hyper& h = a.hp[s.hyper];
-                adamw_vec(pv.lo, avg.lo, mv.lo, vv.lo, h, s.wd);
-                adamw_vec(pv.hi, avg.hi, mv.hi, vv.hi, h, s.wd);
-                st_stream8(s.p + off, pv);
-                st_stream8(s.m + off, mv);
-                st_stream8(s.v + off, vv);
-            }
-        } else {
-            stage_gather(ah, slot, c, prefix, t + D, t1, src, e);
-            do_tile<W, ADAM, GATHER>(s, a, c, t, me, nullptr, 0, unused);
-        }
-    }
-    cp_async_wait<0>();
 }
 
 // ---------------------------------------------------------------- flag barriers
@@ -815,16 +468,11 @@ __device__ __forceinline__ void stamp(const RankCtx& c, int block, int i) {
 
 // ---------------------------------------------------------------- kernels
 
-// The ring of stages behind the tile prefix in dynamic shared memory.
-__device__ __forceinline__ float* ring_of(int* s_prefix, int nseg) {
-    return reinterpret_cast<float*>(reinterpret_cast<char*>(s_prefix) + prefix_smem_bytes(nseg));
-}
-
 // Resident blocks per SM the single-rank kernel is compiled for (80 registers per thread).
 constexpr int kLocalBlocksPerSm = 3;
-template <int W, bool ADAM, int AHEAD>
+template <int W, bool ADAM>
 __global__ void __launch_bounds__(kThreads, W == 1 ? kLocalBlocksPerSm : 2) k_twoshot(const __grid_constant__ LaunchArgs a) {
-    extern __shared__ __align__(128) int s_prefix[];  // tile prefix, then (AHEAD_SMEM) the ring of stages
+    extern __shared__ int s_prefix[];
     __shared__ int s_abort;
     __shared__ double s_red[kThreads / 32 + 1];
     const int G = a.blocks_per_rank;
@@ -861,13 +509,7 @@ __global__ void __launch_bounds__(kThreads, W == 1 ? kLocalBlocksPerSm : 2) k_tw
         stamp(c, b, 1);
         {   // own chunk: reduce, scale, update
             const int cb = cut(T, me, W), ce = cut(T, me + 1, W), L = ce - cb;
-            const int r0 = cb + cut(L, b, G), r1 = cb + cut(L, b + 1, G);
-            if (s_abort) {
-            } else if constexpr (AHEAD == AHEAD_SMEM && W <= kStagedReduceMaxWorld) {
-                reduce_run_staged<W, ADAM>(a, c, s_prefix, ring_of(s_prefix, nseg), r0, r1, me, s_red);
-            } else {
-                reduce_run<W, ADAM, AHEAD>(a, c, s_prefix, r0, r1, me, s_red);
-            }
+            if (!s_abort) reduce_run<W, ADAM>(a, c, s_prefix, cb + cut(L, b, G), cb + cut(L, b + 1, G), me, s_red);
         }
         stamp(c, b, 2);
         post<W>(c, B_REDUCED, b, me, a.seq);
@@ -875,13 +517,7 @@ __global__ void __launch_bounds__(kThreads, W == 1 ? kLocalBlocksPerSm : 2) k_tw
             const int src = (me + k) % W;
             await<W>(c, a, B_REDUCED, b, me, src, ST_TIMEOUT_REDUCED, &s_abort);
             const int cb = cut(T, src, W), ce = cut(T, src + 1, W), L = ce - cb;
-            const int r0 = cb + cut(L, b, G), r1 = cb + cut(L, b + 1, G);
-            if (s_abort) {
-            } else if constexpr (AHEAD == AHEAD_SMEM) {
-                gather_run_staged<W, ADAM>(a, c, s_prefix, ring_of(s_prefix, nseg), r0, r1, me, src);
-            } else {
-                gather_run<W, ADAM, AHEAD>(a, c, s_prefix, r0, r1, me, src);
-            }
+            if (!s_abort) do_run<W, ADAM, GATHER>(a, c, s_prefix, cb + cut(L, b, G), cb + cut(L, b + 1, G), me, src, nullptr, 0);
         }
         stamp(c, b, 3);
         // nobody may reuse or free gradient memory that a peer is still reading
@@ -978,28 +614,13 @@ __global__ void __launch_bounds__(kThreads) k_sumsq_slices(int nslices, const Su
 // ---------------------------------------------------------------- launch
 
 template <int W, bool ADAM>
-static void (*kernel_of(int kind, int ahead))(const LaunchArgs) {
-    if (kind == KERNEL_ONESHOT) return k_oneshot<W, ADAM>;
-    if (W > 1 && ahead == AHEAD_REGS) return k_twoshot<W, ADAM, (W > 1 ? AHEAD_REGS : AHEAD_NONE)>;
-    if (W > 1 && ahead == AHEAD_SMEM) return k_twoshot<W, ADAM, (W > 1 ? AHEAD_SMEM : AHEAD_NONE)>;
-    return k_twoshot<W, ADAM, AHEAD_NONE>;
-}
-
-// More than 48 KiB of dynamic shared memory has to be allowed per kernel, once.
-static bool allow_smem(const void* kern, size_t smem) {
-    if (smem <= 48 * 1024) return true;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxStepSmem) != cudaSuccess) {
-        cudaGetLastError();
-        return false;
-    }
-    return true;
+static void (*kernel_of(int kind))(const LaunchArgs) {
+    return kind == KERNEL_ONESHOT ? k_oneshot<W, ADAM> : k_twoshot<W, ADAM>;
 }
 
 template <int W, bool ADAM>
-static cudaError_t launch_w(int kind, int ahead, bool cooperative, int grid, size_t smem, const LaunchArgs& a,
-                            cudaStream_t st) {
-    void (*kern)(const LaunchArgs) = kernel_of<W, ADAM>(kind, ahead);
-    if (!allow_smem((const void*)kern, smem)) return cudaErrorInvalidValue;
+static cudaError_t launch_w(int kind, bool cooperative, int grid, size_t smem, const LaunchArgs& a, cudaStream_t st) {
+    void (*kern)(const LaunchArgs) = kernel_of<W, ADAM>(kind);
     if (cooperative) {
         void* params[] = {const_cast<LaunchArgs*>(&a)};
         return cudaLaunchCooperativeKernel((const void*)kern, dim3(grid), dim3(kThreads), params, smem, st);
@@ -1009,10 +630,9 @@ static cudaError_t launch_w(int kind, int ahead, bool cooperative, int grid, siz
 }
 
 template <int W, bool ADAM>
-static int occupancy_w(int kind, int ahead, size_t smem) {
+static int occupancy_w(int kind, size_t smem) {
     int n = 0;
-    void (*kern)(const LaunchArgs) = kernel_of<W, ADAM>(kind, ahead);
-    if (!allow_smem((const void*)kern, smem)) return 0;
+    void (*kern)(const LaunchArgs) = kernel_of<W, ADAM>(kind);
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, (const void*)kern, kThreads, smem) != cudaSuccess) return 0;
     return n;
 }
@@ -1029,21 +649,14 @@ static int occupancy_w(int kind, int ahead, size_t smem) {
         case 8: return adam ? fn<8, true>(__VA_ARGS__) : fn<8, false>(__VA_ARGS__); \
     }
 
-int launch_step(int world, bool adam, int kind, int ahead, bool cooperative, int grid, size_t smem, const LaunchArgs& a,
-                cudaStream_t st) {
-    SLB_DISPATCH(world, launch_w, kind, ahead, cooperative, grid, smem, a, st)
+int launch_step(int world, bool adam, int kind, bool cooperative, int grid, size_t smem, const LaunchArgs& a, cudaStream_t st) {
+    SLB_DISPATCH(world, launch_w, kind, cooperative, grid, smem, a, st)
     return (int)cudaErrorInvalidValue;
 }
 
-int step_occupancy(int world, bool adam, int kind, int ahead, size_t smem) {
-    SLB_DISPATCH(world, occupancy_w, kind, ahead, smem)
+int step_occupancy(int world, bool adam, int kind, size_t smem) {
+    SLB_DISPATCH(world, occupancy_w, kind, smem)
     return 0;
-}
-
-size_t step_smem(int world, int kind, int ahead, int nseg) {
-    const size_t prefix = prefix_smem_bytes(nseg);
-    if (world > 1 && kind == KERNEL_PLAIN && ahead == AHEAD_SMEM) return prefix + kRingBytes;
-    return prefix;
 }
 
 static int flat_grid(int64_t n) {
@@ -1179,8 +792,8 @@ extern "C" int slb_adamw_step_static(int nseg, float* const* p, const float* con
     if (cudaGetDevice(&device) != cudaSuccess ||
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
         return -3;
-    const size_t smem = step_smem(1, KERNEL_PLAIN, AHEAD_NONE, nseg);
-    const int per_sm = step_occupancy(1, true, KERNEL_PLAIN, AHEAD_NONE, smem);
+    const size_t smem = (size_t)(nseg + 1) * sizeof(int);
+    const int per_sm = step_occupancy(1, true, KERNEL_PLAIN, smem);
     if (per_sm < 1 || sms < 1) return -3;
     const int64_t cap = (int64_t)per_sm * sms;
     LaunchArgs a{};
@@ -1192,7 +805,7 @@ extern "C" int slb_adamw_step_static(int nseg, float* const* p, const float* con
     h.rbc1 = 1.0 / h.bc1, h.rbc2 = 1.0 / h.bc2;
     h.lr = lr, h.b1 = b1, h.b2 = b2, h.eps = eps, h.c1 = 1 - b1, h.c2 = 1 - b2;
     a.cyclic = 0;
-    if (launch_step(1, true, KERNEL_PLAIN, AHEAD_NONE, false, a.blocks_per_rank, smem, a, 0) != 0) return -3;
+    if (launch_step(1, true, KERNEL_PLAIN, false, a.blocks_per_rank, smem, a, 0) != 0) return -3;
     engine_count_launch();
     return 0;
 }

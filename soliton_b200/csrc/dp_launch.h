@@ -16,20 +16,9 @@ enum KernelKind : int {
 // Launches one kernel of the family for `world` ranks. `grid` = blocks_per_rank x (virtual ranks in this launch);
 // `cooperative` asks the driver to guarantee that all blocks are resident at once (required when several virtual
 // ranks, which wait on one another, share one GPU). Returns a cudaError_t value.
-// `ahead`: how the two-shot kernel runs its peer loads ahead of the arithmetic (same bits whichever).
-enum Ahead_ : int { AHEAD_NONE = 0, AHEAD_REGS = 1, AHEAD_SMEM = 2 };
-constexpr int kRingStages = 7;                                    // tile-sized stages of the shared-memory ring
-constexpr size_t kRingBytes = size_t(kRingStages) * kTile * 4;    // 56 KiB per block
-constexpr size_t kMaxStepSmem = 96 * 1024;                        // ring + tile prefix of up to kMaxSegs segments
-// Bytes the tile prefix of nseg segments takes at the start of dynamic shared memory (the ring follows, aligned).
-__host__ __device__ constexpr size_t prefix_smem_bytes(int nseg) { return (((size_t)nseg + 1) * 4 + 127) & ~size_t(127); }
-static_assert(prefix_smem_bytes(kMaxSegs) + kRingBytes <= kMaxStepSmem, "shared memory of the staged two-shot kernel");
-int launch_step(int world, bool adam, int kind, int ahead, bool cooperative, int grid, size_t smem, const LaunchArgs& a,
-                cudaStream_t st);
+int launch_step(int world, bool adam, int kind, bool cooperative, int grid, size_t smem, const LaunchArgs& a, cudaStream_t st);
 // Resident blocks per SM of that kernel variant.
-int step_occupancy(int world, bool adam, int kind, int ahead, size_t smem);
-// Dynamic shared memory of a launch.
-size_t step_smem(int world, int kind, int ahead, int nseg);
+int step_occupancy(int world, bool adam, int kind, size_t smem);
 // The engine's side of an entry point that launches on its own: first everything the engine has recorded and not yet
 // launched goes out (nothing happens while no device is initialised), afterwards the launch is counted.
 void engine_flush_pending();

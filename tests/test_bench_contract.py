@@ -22,7 +22,7 @@ def run_bench(*args):
 
 
 def test_reference_arm_prints_one_contract_line(built):
-    d = run_bench("--impl", "reference", "--steps", "2", "--warmup", "1")
+    d = run_bench("--impl", "reference", "--steps", "2", "--warmup", "1", "--flat", str(64 << 20))
     assert BASE_KEYS <= set(d) and d["impl"] == "reference"
     assert d["metric"] == "fused_allreduce_adamw_algorithmic_GBps" and d["unit"] == "GB/s" and d["value"] > 0
     assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] == 1
@@ -40,7 +40,7 @@ def test_reference_arm_under_torchrun_only_rank_zero_reports(built):
     s.close()
     out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
                           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "bench.py"),
-                          "--impl", "reference", "--gpus", "2", "--steps", "2", "--warmup", "1"],
+                          "--impl", "reference", "--gpus", "2", "--steps", "2", "--warmup", "1", "--flat", str(64 << 20)],
                          capture_output=True, text=True, timeout=600, cwd=ROOT)
     assert out.returncode == 0, out.stderr[-2000:]
     lines = [json.loads(l) for l in out.stdout.splitlines() if l.startswith("{")]

@@ -132,3 +132,37 @@ def test_back_to_back_host_fed_steps_order_themselves(cuda):
         for i, buf in enumerate(hp[k]):
             np.testing.assert_array_equal(buf.array, ref[i][0])
     T.synchronize()
+
+
+def test_each_rank_reads_back_only_its_share_of_the_parameters(cuda):
+    """Data-parallel ranks end a step with the same parameter bits; a host-fed job therefore reads every parameter
+    back once, rank r its r-th share. Emulated here by binding the same optimizer as rank r of 4, for every r: the
+    shares are disjoint, cover everything, and hold the right values."""
+    world = 4
+    rng, params, opt, ref = make(bucket_bytes=256 << 10)
+    for p in params:
+        p.grad = T.empty(p.shape, "cuda")
+    hg = [Pinned(p.numel) for p in params]
+    grads = [(rng.standard_normal(s) * 1e-3).astype(np.float32) for s in SHAPES]
+    for buf, g in zip(hg, grads):
+        buf.array[:] = g.ravel()
+    opt.bind_host(hg, [Pinned(p.numel) for p in params])
+    opt.host_step()
+    oracle_step(ref, grads, 1)
+    written = [np.zeros(p.numel, np.int32) for p in params]
+    total = 0
+    for r in range(world):
+        hp = [Pinned(p.numel) for p in params]
+        for buf in hp:
+            buf.array[:] = np.nan
+        opt.bind_host(hg, hp, share=(r, world))
+        total += opt.download_bytes
+        for b in range(len(opt.buckets)):
+            opt.download(b)
+        assert lib.slb_wait_copies() == 0
+        for i, buf in enumerate(hp):
+            got = ~np.isnan(buf.array)
+            written[i] += got
+            np.testing.assert_array_equal(buf.array[got], ref[i][0][got])
+    assert all((w == 1).all() for w in written)          # every element exactly once over the four ranks
+    assert total == 4 * sum(p.numel for p in params)

@@ -38,12 +38,10 @@ def oracle_steps(p0, g_by_step, sizes, wds, world):
     return ref, means
 
 
-@pytest.fixture(params=[0, 1, 2], ids=["loads-on-demand", "register-ring", "shared-memory-ring"])
-def large_kernel(request):
-    """Runs a test once with each way the two-shot kernel can run its peer loads ahead of the arithmetic."""
-    set_option("prefetch", request.param)
-    yield request.param
-    set_option("prefetch", 0)
+@pytest.fixture
+def large_kernel():
+    """The kernel that takes large steps (two-shot); kept as a fixture so that variants can be run side by side."""
+    return "k_twoshot"
 
 
 @pytest.mark.parametrize("mode", [1, 2], ids=["oneshot", "twoshot"])
