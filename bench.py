@@ -39,13 +39,18 @@ sys.path.insert(0, ROOT)
 METRIC = "fused_allreduce_adamw_algorithmic_GBps"
 BYTES_PER_PARAM = 28            # algorithmic HBM bytes per parameter per rank
 NVLINK_NOMINAL_GBS = 900.0      # per direction per GPU
-# What `bench.py --fabric` measured on this pool's 8 x B200 boxes when every GPU exchanges with every other at once
-# (GB/s received per GPU, the slowest GPU): by a kernel pulling with 256-bit loads, and by the copy engines.
-# None: not measured yet for that world size.
-FABRIC_MEASURED_GBS = {2: None, 4: None, 8: None}
+NVLINK_ONE_WAY_GBS = 770.0      # this pool's peer-copy figure with the links loaded one way (the fabric probe of this file
+                                # gives 718-753 to a pulling kernel and up to 792 to the copy engines in that case)
+# What `bench.py --fabric` measured on this pool's 8 x B200 boxes when every GPU exchanges with every other at once, so
+# that every link carries data both ways as in an all-reduce: GB/s per GPU, the slowest GPU of the group, by a kernel
+# pulling with 256-bit loads (what the two-shot exchange does), by a kernel pushing with 256-bit stores, and with
+# every link loaded one way only.
+FABRIC_MEASURED_GBS = {2: {"sm_pull": 615.6, "sm_push": 657.3, "sm_pull_one_direction": 718.4},
+                       4: {"sm_pull": 631.4, "sm_push": 677.5, "sm_pull_one_direction": 730.0},
+                       8: {"sm_pull": 641.1, "sm_push": 684.9, "sm_pull_one_direction": 737.8}}
 FALLBACK_HBM_GBS = 6650.0       # used only when MEASURED_PEAKS.json is absent
 # DRAM bytes per parameter of the dominant kernel from an ncu capture, per world size; None = not captured
-NCU_DRAM_BYTES_PER_PARAM = {1: 27.22}
+NCU_DRAM_BYTES_PER_PARAM = {1: 27.31}
 # A small tensor set for the checked run: 1.6 M floats, above the one-shot staging slot at every world size
 PARITY_SHAPES = [(1000, 1200), (1200,), (300, 1000), (1000,), (3,), (2048 * 50,)]
 
@@ -551,7 +556,7 @@ def run_ours(args, rank, local_rank, world):
     t_hbm = BYTES_PER_PARAM * P / (hbm * 1e9)
     nvl_bytes = 8.0 * P * (world - 1) / world
     fabric = FABRIC_MEASURED_GBS.get(world)
-    t_nvl = nvl_bytes / (NVLINK_NOMINAL_GBS * 1e9)
+    t_nvl = nvl_bytes / (NVLINK_ONE_WAY_GBS * 1e9)
     kernel = {0: "k_twoshot<1,adam>", 1: f"k_oneshot<{world},adam>", 2: f"k_twoshot<{world},adam>"}[mode]
     if args.bare:
         kernel = kernel.replace(",adam>", ",mean only>")
@@ -561,9 +566,11 @@ def run_ours(args, rank, local_rank, world):
                 "traffic": traffic * P if traffic else None, "peak_source": f"{hbm_kind} HBM copy"}
     else:
         nvl = nvl_bytes / (ms * 1e-3) / 1e9
-        roof = {"bound": "nvlink", "achieved": nvl, "peak": NVLINK_NOMINAL_GBS, "unit": "GB/s", "frac": nvl / NVLINK_NOMINAL_GBS,
-                "traffic": traffic * P if traffic else None, "peak_source": "nominal NVLink 5, per direction per GPU",
-                "fabric_measured": fabric, "frac_of_fabric_measured": nvl / fabric["sm_pull"] if fabric else None,
+        roof = {"bound": "nvlink", "achieved": nvl, "peak": NVLINK_ONE_WAY_GBS, "unit": "GB/s", "frac": nvl / NVLINK_ONE_WAY_GBS,
+                "traffic": traffic * P if traffic else None,
+                "peak_source": "peer copy per direction per GPU with the links loaded one way (nominal 900)",
+                "frac_of_nominal_900": nvl / NVLINK_NOMINAL_GBS,
+                "fabric_measured_two_way": fabric, "frac_of_fabric_measured_two_way": nvl / fabric["sm_pull"] if fabric else None,
                 "hbm_achieved": hbm_per_rank, "hbm_peak": hbm, "hbm_frac": hbm_per_rank / hbm}
     roof.update({"kernel": kernel, "ms_per_launch": ms / max(launches / args.steps, 1), "roofline_ms": 1e3 * max(t_hbm, t_nvl),
                  "frac_of_roofline_time": max(t_hbm, t_nvl) / (ms * 1e-3)})

@@ -122,6 +122,13 @@ int sl_cuda_nccl_init(int rank, int world, const char* id128);
 int sl_cuda_nccl_group(int start);
 int sl_cuda_nccl_allreduce_mean(float* p, int64_t n);
 void sl_cuda_nccl_destroy(void);
+/* core/soliton/api.d:26-29 -> core/cuda/kernels.cu:200,212,219-224: the small ops the trainer runs between the
+ * gradient mean and the step (gradient accumulation, clipping). Linking these as well lets the clip ride along with
+ * the path: the sums of squares come out of the gradient mean's launch, in-place scales are applied by the AdamW
+ * launch. sl_cuda_sumsq blocks, like the reference's. */
+void sl_cuda_axpy(const float* x, float* y, int64_t n, float alpha);
+void sl_cuda_scale(const float* x, float* y, int64_t n, float alpha);
+double sl_cuda_sumsq(const float* x, int64_t n);
 /* No counterpart in the reference; modelled on sl_cuda_set_workspace (core/cuda/kernels.cu:115). A host core that
  * owns the allocator hands the path its workspace (slb_workspace_bytes() bytes from its pool) once per device. */
 int sl_cuda_dp_set_workspace(void* p, size_t n);

@@ -4,7 +4,8 @@ to check the product's C++ pool counter by counter on random traces. Nothing in 
 Restated line by line from alloc.d: roundSize :54-60, mix :62-66, rawAlloc :68-86 (limit check against reserved),
 arenaAlloc :98-111, alloc :128-174 (exact-size cache scanned front to back, swap-remove; one flush-and-retry),
 release :176-200, releaseArena :204-213, emptyCache :215-223; and the stats / reset of api.d:143-164.
-Addresses are modelled as opaque tokens: they do not enter any statistic.
+Addresses are modelled as tokens, one per raw block: the test checks that the library hands the cached blocks out in
+the same order as this model does.
 """
 MASK = (1 << 64) - 1
 FNV_SEED, FNV_PRIME = 1469598103934665603, 1099511628211

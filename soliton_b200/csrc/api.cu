@@ -189,6 +189,9 @@ int sl_cuda_nccl_group(int start) { return E().group(start); }
 int sl_cuda_nccl_allreduce_mean(float* p, int64_t n) { return E().allreduce_mean(p, n); }
 void sl_cuda_nccl_destroy(void) { E().dist_destroy(); }
 int sl_cuda_dp_set_workspace(void* p, size_t n) { return E().adopt_workspace(p, n); }
+void sl_cuda_axpy(const float* x, float* y, int64_t n, float alpha) { E().axpy(x, y, n, alpha); }
+void sl_cuda_scale(const float* x, float* y, int64_t n, float alpha) { E().scale(x, y, n, alpha); }
+double sl_cuda_sumsq(const float* x, int64_t n) { return E().sumsq(x, n); }
 
 // ---- additions
 

@@ -155,17 +155,20 @@ __device__ __forceinline__ double sqrt_exact(double x) {
 // is promoted, one final rounding of p to float.
 // A gradient beyond about 1.8e19 overflows the float second moment to +inf. IEEE arithmetic then gives
 // sqrt(inf) = inf and m / (inf + eps) = a zero with the sign of m (NaN when m is infinite too), where the Newton
-// steps above would give NaN; that one case is decided on the float v and patched in with a select.
+// steps above would give NaN. That one case is decided on the float v and patched in with selects: the quotient
+// becomes -0 (the neutral element of addition, signs included) and the signed zero, or NaN, of m * 0 is added to
+// wd * p in float, which is exact.
 __device__ __forceinline__ void adamw_elem(float& p, float g, float& m, float& v, const Hyper& h, float wd) {
     m = __fmaf_rn(h.b1, m, __fmul_rn(h.c1, g));
     v = __fmaf_rn(h.b2, v, __fmul_rn(__fmul_rn(h.c2, g), g));
+    const bool overflowed = v == __int_as_float(0x7f800000);
+    const float wdp = __fmul_rn(wd, p);
+    const double decay = (double)(overflowed ? __fadd_rn(__fmul_rn(m, 0.0f), wdp) : wdp);
     const double mh = div_by_const((double)m, h.bc1, h.rbc1);
     const double vh = div_by_const((double)v, h.bc2, h.rbc2);
-    const double decay = (double)__fmul_rn(wd, p);
-    double x = __dadd_rn(div_exact(mh, __dadd_rn(sqrt_exact(vh), (double)h.eps)), decay);
-    const double x_overflowed = __dadd_rn((double)__fmul_rn(m, 0.0f), decay);
-    x = v == __int_as_float(0x7f800000) ? x_overflowed : x;
-    p = __double2float_rn(__fma_rn(-(double)h.lr, x, (double)p));
+    double q = div_exact(mh, __dadd_rn(sqrt_exact(vh), (double)h.eps));
+    q = overflowed ? -0.0 : q;
+    p = __double2float_rn(__fma_rn(-(double)h.lr, __dadd_rn(q, decay), (double)p));
 }
 __device__ __forceinline__ void adamw_vec(float4& p, const float4& g, float4& m, float4& v, const Hyper& h, float wd) {
     adamw_elem(p.x, g.x, m.x, v.x, h, wd);

@@ -84,11 +84,15 @@ void* Pool::alloc(size_t n) {
         return reinterpret_cast<void*>(4096 + idx * 64);
     }
     void* p = nullptr;
-    auto hit = cache_.find(n);
-    if (hit != cache_.end() && !hit->second.empty()) {
-        p = hit->second.back();
-        hit->second.pop_back();
-    } else {
+    for (size_t i = 0; i < cache_.size(); i++) {  // alloc.d:145-151: first exact fit; the last entry takes its place
+        if (cache_[i].size == n) {
+            p = cache_[i].ptr;
+            cache_[i] = cache_.back();
+            cache_.pop_back();
+            break;
+        }
+    }
+    if (!p) {
         p = raw_alloc(n);
         if (!p) {
             empty_cache();  // alloc.d:158-162: one flush-and-retry, exactly as a real allocator under pressure
@@ -118,7 +122,7 @@ void Pool::release(void* p, size_t n) {
         if (idx < rec_size_.size()) rec_end_[idx] = (int64_t)rec_size_.size();
         return;
     }
-    cache_[n].push_back(p);
+    cache_.push_back(Cached{n, p});
 }
 
 // alloc.d:204-213
@@ -132,12 +136,9 @@ void Pool::release_arena() {
 
 // alloc.d:215-223
 void Pool::empty_cache() {
-    for (auto& kv : cache_) {
-        for (void* p : kv.second) {
-            raw_free(p);
-            reserved_ -= (int64_t)kv.first;
-        }
-        kv.second.clear();
+    for (const Cached& b : cache_) {
+        raw_free(b.ptr);
+        reserved_ -= (int64_t)b.size;
     }
     cache_.clear();
 }

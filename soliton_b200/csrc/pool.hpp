@@ -4,9 +4,10 @@
 // exact-size block cache, the same FNV-1a trace hash over (kind, rounded size) events, the same reserve limit with
 // one flush-and-retry, the same trace recording and arena replay. Because the policy depends only on the sequence
 // of requested sizes, the meta pool (fake addresses, no memory) reports the byte counts the cuda pool will see.
-// The data structures are this library's own: the cache is a size -> LIFO stack map instead of a scanned array
-// (which block of a given size is handed out does not enter any statistic), and the cuda pool keeps a registry of
-// the raw blocks it owns so that the data-parallel engine can export them to peer processes.
+// The cache hands blocks out in the reference's order too (the first block of the exact size, whose place the last
+// cached block then takes, alloc.d:145-151), so that the sequence of addresses a run sees is the reference's. The cuda
+// pool additionally keeps a registry of the raw blocks it owns, so that the data-parallel engine can export them to
+// peer processes.
 #pragma once
 #include <cstddef>
 #include <cstdint>
@@ -82,7 +83,11 @@ private:
     static constexpr size_t kMaxMarks = 64;
 
     int dev_;
-    std::unordered_map<size_t, std::vector<void*>> cache_;
+    struct Cached {
+        size_t size;
+        void* ptr;
+    };
+    std::vector<Cached> cache_;   // in release order, holes filled from the back (alloc.d:145-151, 199)
     int64_t allocated_ = 0, reserved_ = 0, peak_allocated_ = 0, peak_reserved_ = 0, n_alloc_ = 0, n_raw_ = 0;
     int64_t limit_ = 0;
     uint64_t hash_ = kHashSeed;

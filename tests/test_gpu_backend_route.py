@@ -53,6 +53,17 @@ for step in (1, 2, 3):
             got = np.empty(n, np.float32)
             rt.d2h(got, ptr)
             assert np.array_equal(got, want)
+# the small ops around the path at backend level: Sum x^2 (blocking), in-place scale, axpy
+g = grads[2]
+got = lib.sl_cuda_sumsq(dev[2][3], sizes[2])
+assert abs(got - float(np.sum(g.astype(np.float64) ** 2))) <= 1e-12 * got
+lib.sl_cuda_scale(dev[2][3], dev[2][3], sizes[2], 0.5)
+lib.sl_cuda_axpy(dev[2][3], dev[2][3], sizes[2], 2.0)             # g <- 0.5 g + 2 (0.5 g)
+lib.slb_flush()
+out = np.empty(sizes[2], np.float32)
+rt.d2h(out, dev[2][3])
+half = g * np.float32(0.5)
+assert np.array_equal(out, half + np.float32(2.0) * half)
 assert lib.sl_check(2) == 0
 print("route ok")
 '''

@@ -160,13 +160,16 @@ def test_init_device_reserves_the_same_on_meta_each_time(clean):
 @pytest.mark.parametrize("seed", [0, 1, 2])
 def test_random_traces_match_the_restated_reference_policy(clean, dev, seed):
     """Differential test against oracle/pool_model.py (alloc.d restated in Python): every counter after every
-    operation, including reserve-limit refusals, flush-and-retry, cache flushes and statistic resets."""
+    operation, including reserve-limit refusals, flush-and-retry, cache flushes and statistic resets -- and WHICH
+    cached block an allocation gets (the reference takes the first of the exact size and moves the last cached
+    block into its place, alloc.d:145-151), checked through a token <-> address correspondence."""
     from oracle.pool_model import PoolModel
     lib = clean
     rng = np.random.default_rng(seed)
     base = stats(lib, dev)
     model = PoolModel()
     live = []
+    address_of = {}      # model token -> address the library gave for it
     sizes = [int(x) for x in rng.choice([1, 300, 512, 4096, 70000, 1 << 20, (1 << 20) + 5, 3 << 20, 9 << 20], 400)]
     for step, n in enumerate(sizes):
         op = rng.random()
@@ -174,6 +177,7 @@ def test_random_traces_match_the_restated_reference_policy(clean, dev, seed):
             p, tok = lib.sl_alloc(dev, n), model.alloc(n)
             assert bool(p) == (tok is not None)
             if p:
+                assert address_of.setdefault(tok, p) == p, (step, "the library reused another cached block than the reference would")
                 live.append((p, tok, n))
         elif op < 0.9:
             p, tok, m = live.pop(int(rng.integers(len(live))))
@@ -182,6 +186,7 @@ def test_random_traces_match_the_restated_reference_policy(clean, dev, seed):
         elif op < 0.94:
             lib.sl_empty_cache(dev)
             model.empty_cache()
+            address_of = {tok: p for p, tok, _ in live}   # cached blocks went back to the system
         elif op < 0.97:
             lib.sl_reset_stats(dev)
             model.reset_stats()
