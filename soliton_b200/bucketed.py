@@ -87,6 +87,7 @@ class BucketedAdamW(AdamW):
         tensor -- into the same places of its host buffers; the rest of those buffers is not written."""
         addr = lambda x: x.data_ptr() if hasattr(x, "data_ptr") else int(x)  # noqa: E731
         rank, world = share if share else (0, 1)
+        self._bound = (list(host_grads), list(host_params))   # the copies run later: the buffers must outlive this call
         self._up, self._down = [], []
         self.upload_bytes = self.download_bytes = 0
         for bucket in self.buckets:

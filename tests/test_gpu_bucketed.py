@@ -146,9 +146,12 @@ def test_each_rank_reads_back_only_its_share_of_the_parameters(cuda):
     grads = [(rng.standard_normal(s) * 1e-3).astype(np.float32) for s in SHAPES]
     for buf, g in zip(hg, grads):
         buf.array[:] = g.ravel()
-    opt.bind_host(hg, [Pinned(p.numel) for p in params])
+    whole = [Pinned(p.numel) for p in params]
+    opt.bind_host(hg, whole)
     opt.host_step()
     oracle_step(ref, grads, 1)
+    for i, buf in enumerate(whole):
+        np.testing.assert_array_equal(buf.array, ref[i][0])
     written = [np.zeros(p.numel, np.int32) for p in params]
     total = 0
     for r in range(world):
