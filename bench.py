@@ -76,6 +76,7 @@ def parse():
     ap.add_argument("--sweep", action="store_true", help="bucket-size sweep 4 KB .. 1 GB, one-shot vs two-shot (N >= 2)")
     ap.add_argument("--fabric", action="store_true", help="NVLink fabric ceiling: copy engines and kernels, one and both directions")
     ap.add_argument("--bare", action="store_true", help="gradient mean only, no optimizer update (link-bound floor)")
+    ap.add_argument("--layernorm", action="store_true", help="layer normalisation forward and backward against the reference's kernels")
     return ap.parse_args()
 
 
@@ -696,6 +697,62 @@ def run_fabric(args):
     print(json.dumps({"metric": "nvlink_fabric_GBps_per_direction_per_gpu", "gpus_visible": have, "rows": rows}), flush=True)
 
 
+def run_layernorm(args):
+    """Layer normalisation, forward and backward, this library's kernels and the reference's (core/cuda/kernels.cu
+    :385-449 from oracle/_ref/) on the same buffers: 65,536 rows of 768 and of 1024 floats (201 / 268 MB per tensor,
+    larger than L2), CUDA events, median of 20. GB/s are algorithmic: 8 bytes per element forward (read x, write y),
+    12 backward (read dy and x, write dx)."""
+    import numpy as np
+    import torch
+    from soliton_b200 import tensor as T
+    from soliton_b200._C import lib
+    T._dev(T.CUDA)
+    R = reference_gpu_lib()
+    C = ctypes
+    if R is not None:
+        assert R.sl_cuda_set_device(0) == 0
+        R.sl_cuda_layernorm.argtypes = [C.c_void_p] * 6 + [C.c_int64, C.c_int64, C.c_float, C.c_void_p]
+        R.sl_cuda_layernorm_bwd.argtypes = [C.c_void_p] * 8 + [C.c_int64, C.c_int64] + [C.c_void_p] * 5
+    hbm, hbm_kind = hbm_peak()
+
+    def timed(fn, reps=20):
+        out = []
+        for i in range(reps + 3):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            if i >= 3:
+                out.append(e0.elapsed_time(e1))
+        return statistics.median(out)
+
+    rows_out = []
+    for rows, c in ((65536, 768), (65536, 1024), (8192, 768)):
+        rng = np.random.default_rng(0)
+        x = T.tensor(rng.standard_normal((rows, c), dtype=np.float32), "cuda")
+        dy = T.tensor(rng.standard_normal((rows, c), dtype=np.float32), "cuda")
+        w, b = T.tensor(np.ones(c, np.float32), "cuda"), T.zeros((c,), "cuda")
+        y, dx, tmp = T.empty((rows, c), "cuda"), T.empty((rows, c), "cuda"), T.empty((rows, c), "cuda")
+        mean, invstd, sg, sgx, ones_r = (T.empty((rows,), "cuda") for _ in range(5))
+        dw, db, ones_c = (T.empty((c,), "cuda") for _ in range(3))
+        T.synchronize()
+        for name, L in (("this library", lib), ("reference", R)):
+            if L is None:
+                continue
+            fwd = lambda: L.sl_cuda_layernorm(x.ptr, w.ptr, b.ptr, y.ptr, mean.ptr, invstd.ptr, rows, c, 1e-5, ones_c.ptr)  # noqa: E731
+            bwd = lambda: L.sl_cuda_layernorm_bwd(dy.ptr, x.ptr, w.ptr, mean.ptr, invstd.ptr, dx.ptr, dw.ptr, db.ptr, rows, c,  # noqa: E731
+                                                  tmp.ptr, sg.ptr, sgx.ptr, ones_c.ptr, ones_r.ptr)
+            tf, tb = timed(fwd), timed(bwd)
+            n = rows * c
+            rows_out.append({"rows": rows, "c": c, "by": name, "fwd_ms": round(tf, 4), "bwd_ms": round(tb, 4),
+                             "fwd_GBps": round(8 * n / tf / 1e6, 1), "bwd_GBps": round(12 * n / tb / 1e6, 1),
+                             "fwd_frac_of_hbm": round(8 * n / tf / 1e6 / hbm, 3), "bwd_frac_of_hbm": round(12 * n / tb / 1e6 / hbm, 3)})
+        assert lib.sl_check(T.CUDA) == 0
+    print(json.dumps({"metric": "layernorm_algorithmic_GBps", "hbm_peak": hbm, "hbm_peak_kind": hbm_kind, "rows": rows_out}), flush=True)
+
+
 def run_reference_gpu(args, rank, local_rank, world):
     """The reference's own GPU path as an arm of its own (the product arm also carries it as `gpu_baseline`)."""
     import torch
@@ -728,6 +785,8 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", 1))
     if args.fabric:
         return run_fabric(args)
+    if args.layernorm:
+        return run_layernorm(args)
     if world == 1 and args.gpus > 1:
         # launched without torchrun: start one process per GPU ourselves
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",

@@ -21,6 +21,7 @@
 #include <cstdlib>
 #include <cstring>
 
+#include "../include/soliton_b200.h"
 #include "../soliton_b200/csrc/dp_engine.hpp"
 #include "../soliton_b200/csrc/foreign_path.h"
 #include "../soliton_b200/csrc/pool.hpp"
@@ -264,6 +265,15 @@ void sl_gelu_bwd(int dev, const float* x, const float* dy, float* dx, int64_t n)
     if (route(dev) == RUN) backend().gelu_bwd(x, dy, dx, n);
 }
 
+// SOLITON_FULLSTEP_LN=reference: layer normalisation from the reference backend instead of this library's kernels.
+static bool reference_layernorm() {
+    static const bool wanted = [] {
+        const char* v = getenv("SOLITON_FULLSTEP_LN");
+        return v && strcmp(v, "reference") == 0;
+    }();
+    return wanted;
+}
+
 // api.d:427-439: ones of c floats
 int sl_layernorm(int dev, const float* x, const float* w, const float* b, float* y, float* mean, float* invstd,
                  int64_t outer, int64_t c, float eps) {
@@ -271,7 +281,12 @@ int sl_layernorm(int dev, const float* x, const float* w, const float* b, float*
     Scratch s(dev);
     float* ones = s.floats(c);
     if (!s.ok) return kOutOfMemory;
-    if (route(dev) == RUN) backend().layernorm(x, w, b, y, mean, invstd, outer, c, eps, ones);
+    if (route(dev) == RUN) {
+        if (reference_layernorm())
+            backend().layernorm(x, w, b, y, mean, invstd, outer, c, eps, ones);
+        else
+            sl_cuda_layernorm(x, w, b, y, mean, invstd, outer, c, eps, ones);
+    }
     return 0;
 }
 
@@ -286,7 +301,12 @@ int sl_layernorm_bwd(int dev, const float* dy, const float* x, const float* w, c
     float* ones_c = s.floats(c);
     float* ones_rows = s.floats(outer);
     if (!s.ok) return kOutOfMemory;
-    if (route(dev) == RUN) backend().layernorm_bwd(dy, x, w, mean, invstd, dx, dw, db, outer, c, tmp, sg, sgx, ones_c, ones_rows);
+    if (route(dev) == RUN) {
+        if (reference_layernorm())
+            backend().layernorm_bwd(dy, x, w, mean, invstd, dx, dw, db, outer, c, tmp, sg, sgx, ones_c, ones_rows);
+        else
+            sl_cuda_layernorm_bwd(dy, x, w, mean, invstd, dx, dw, db, outer, c, tmp, sg, sgx, ones_c, ones_rows);
+    }
     return 0;
 }
 

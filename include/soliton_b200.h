@@ -129,6 +129,16 @@ void sl_cuda_nccl_destroy(void);
 void sl_cuda_axpy(const float* x, float* y, int64_t n, float alpha);
 void sl_cuda_scale(const float* x, float* y, int64_t n, float alpha);
 double sl_cuda_sumsq(const float* x, int64_t n);
+/* core/soliton/api.d:37-41 -> core/cuda/kernels.cu:409-449: layer normalisation over rows of c floats, forward
+ * (y, and the row's mean and 1/std for the backward pass) and backward (dx, and dw, db summed over the rows). One pass
+ * over the activations in each direction. The scratch pointers are the ones the reference's host core passes: only
+ * `tmp` (outer x c floats) is used, for the per-block column sums; `ones`, `sg`, `sgx`, `ones_c`, `ones_rows` may be
+ * NULL. Asynchronous on the legacy stream; a launch failure sets the sticky error 2. */
+void sl_cuda_layernorm(const float* x, const float* w, const float* b, float* y, float* mean, float* invstd, int64_t outer,
+                       int64_t c, float eps, float* ones);
+void sl_cuda_layernorm_bwd(const float* dy, const float* x, const float* w, const float* mean, const float* invstd,
+                           float* dx, float* dw, float* db, int64_t outer, int64_t c, float* tmp, float* sg, float* sgx,
+                           float* ones_c, float* ones_rows);
 /* No counterpart in the reference; modelled on sl_cuda_set_workspace (core/cuda/kernels.cu:115). A host core that
  * owns the allocator hands the path its workspace (slb_workspace_bytes() bytes from its pool) once per device. */
 int sl_cuda_dp_set_workspace(void* p, size_t n);
