@@ -76,6 +76,7 @@ def parse():
     ap.add_argument("--sweep", action="store_true", help="bucket-size sweep 4 KB .. 1 GB, one-shot vs two-shot (N >= 2)")
     ap.add_argument("--fabric", action="store_true", help="NVLink fabric ceiling: copy engines and kernels, one and both directions")
     ap.add_argument("--bare", action="store_true", help="gradient mean only, no optimizer update (link-bound floor)")
+    ap.add_argument("--attention", action="store_true", help="fused causal attention against the reference's TF32 path")
     ap.add_argument("--layernorm", action="store_true", help="layer normalisation forward and backward against the reference's kernels")
     return ap.parse_args()
 
@@ -753,6 +754,70 @@ def run_layernorm(args):
     print(json.dumps({"metric": "layernorm_algorithmic_GBps", "hbm_peak": hbm, "hbm_peak_kind": hbm_kind, "rows": rows_out}), flush=True)
 
 
+def run_attention(args):
+    """Causal attention, forward and backward, this library's fused kernels and the reference's TF32 path
+    (core/cuda/kernels.cu:536-692 from oracle/_ref/ with sl_cuda_set_tf32(1)) on the same buffers, at GPT-2's shapes
+    (batch 8, context 1024, head size 64; 12 and 16 heads), CUDA events, median of 20. TFLOP/s count the causal half
+    of the products only: forward 2 products, backward 5, each 2 * T * T / 2 * 64 flops per head."""
+    import numpy as np
+    import torch
+    from soliton_b200 import tensor as T
+    from soliton_b200._C import lib
+    T._dev(T.CUDA)
+    R = reference_gpu_lib()
+    C = ctypes
+    if R is not None:
+        assert R.sl_cuda_set_device(0) == 0
+        R.sl_cuda_attention.argtypes = [C.c_void_p] * 3 + [C.c_int64] * 4 + [C.c_float, C.c_int64] + [C.c_void_p] * 8
+        R.sl_cuda_attention_bwd.argtypes = [C.c_void_p] * 5 + [C.c_int64] * 4 + [C.c_float, C.c_int64] + [C.c_void_p] * 9
+        R.sl_cuda_set_tf32.argtypes = [C.c_int]
+        R.sl_cuda_set_tf32(1)
+
+    def timed(fn, reps=20):
+        out = []
+        for i in range(reps + 3):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            if i >= 3:
+                out.append(e0.elapsed_time(e1))
+        return statistics.median(out)
+
+    rows_out = []
+    hs, tile = 64, 256
+    for B, Tn, H in ((8, 1024, 12), (8, 1024, 16), (8, 512, 12)):
+        rng = np.random.default_rng(0)
+        bh = B * H
+        rows = bh * tile
+        qkv = T.tensor(rng.standard_normal((B, Tn, 3, H, hs), dtype=np.float32), "cuda")
+        dout = T.tensor(rng.standard_normal((B, Tn, H, hs), dtype=np.float32), "cuda")
+        out, dqkv, Lb = T.empty((B, Tn, H, hs), "cuda"), T.empty((B, Tn, 3, H, hs), "cuda"), T.empty((bh, Tn), "cuda")
+        s, dp = T.empty((rows, tile), "cuda"), T.empty((rows, tile), "cuda")
+        acc, oc = T.empty((rows, hs), "cuda"), T.empty((rows, hs), "cuda")
+        m, l, c = (T.empty((rows,), "cuda") for _ in range(3))
+        rowbuf, ones, ptrs = T.empty((rows, 17), "cuda"), T.empty((tile,), "cuda"), T.empty((18 * bh,), "cuda")
+        T.synchronize()
+        scale = 0.125
+        for name, Lib in (("this library", lib), ("reference, TF32", R)):
+            if Lib is None:
+                continue
+            fwd = lambda: Lib.sl_cuda_attention(qkv.ptr, out.ptr, Lb.ptr, B, Tn, H, hs, scale, tile, s.ptr, acc.ptr, m.ptr, l.ptr,  # noqa: E731
+                                                c.ptr, rowbuf.ptr, ones.ptr, ptrs.ptr)
+            bwd = lambda: Lib.sl_cuda_attention_bwd(qkv.ptr, out.ptr, Lb.ptr, dout.ptr, dqkv.ptr, B, Tn, H, hs, scale, tile, s.ptr,  # noqa: E731
+                                                    dp.ptr, acc.ptr, oc.ptr, m.ptr, l.ptr, rowbuf.ptr, ones.ptr, ptrs.ptr)
+            tf, tb = timed(fwd), timed(bwd)
+            flop = bh * Tn * Tn * hs  # one causal product: 2 * T * T / 2 * hs per head
+            rows_out.append({"B": B, "T": Tn, "H": H, "by": name, "fwd_ms": round(tf, 4), "bwd_ms": round(tb, 4),
+                             "fwd_causal_TFLOPs": round(2 * flop / tf / 1e9, 1), "bwd_causal_TFLOPs": round(5 * flop / tb / 1e9, 1)})
+        assert lib.sl_check(T.CUDA) == 0
+    if R is not None:
+        R.sl_cuda_set_tf32(0)
+    print(json.dumps({"metric": "attention_ms", "rows": rows_out}), flush=True)
+
+
 def run_reference_gpu(args, rank, local_rank, world):
     """The reference's own GPU path as an arm of its own (the product arm also carries it as `gpu_baseline`)."""
     import torch
@@ -787,6 +852,8 @@ def main():
         return run_fabric(args)
     if args.layernorm:
         return run_layernorm(args)
+    if args.attention:
+        return run_attention(args)
     if world == 1 and args.gpus > 1:
         # launched without torchrun: start one process per GPU ourselves
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",

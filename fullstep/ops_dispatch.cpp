@@ -192,13 +192,27 @@ int64_t chunks_for(int64_t dim) {  // api.d:113-119: about sqrt(dim) chunks for 
 size_t sort_temp_bytes(int64_t n) { return (size_t)n * 16 + (size_t(1) << 20); }  // api.d:124-127
 int64_t attention_tile(int64_t T) { return T % 256 == 0 ? 256 : T; }             // core/cuda/kernels.cu:612
 
+// Whether matmuls run with TF32 operands (sl_set_tf32). Attention goes to this library's fused kernels only then:
+// they multiply in TF32, which is the arithmetic the caller asked for in that mode and not otherwise.
+bool g_tf32 = false;
+// SOLITON_FULLSTEP_ATTN=reference: attention from the reference backend in every mode.
+bool fused_attention(int64_t B, int64_t T, int64_t H, int64_t hs, int64_t tile) {
+    static const bool refused = [] {
+        const char* v = getenv("SOLITON_FULLSTEP_ATTN");
+        return v && strcmp(v, "reference") == 0;
+    }();
+    return g_tf32 && !refused && sl_cuda_attention_supported(T, hs) && B * H * T <= B * H * tile * hs;
+}
 }  // namespace
 
 extern "C" {
 
 // api.d:292-297
 void sl_set_tf32(int dev, int on) {
-    if (route(dev) == RUN) backend().set_tf32(on);
+    if (route(dev) == RUN) {
+        backend().set_tf32(on);
+        g_tf32 = on != 0;
+    }
 }
 
 // api.d:335-346
@@ -362,7 +376,9 @@ int sl_attention(int dev, const float* qkv, float* o, float* L, int64_t B, int64
     float* ones = s.floats(tile > hs ? tile : hs);
     void* ptrs = s.bytes((size_t)(5 * bh) * sizeof(void*));
     if (!s.ok) return kOutOfMemory;
-    if (route(dev) == RUN) backend().attention(qkv, o, L, B, T, H, hs, scale, tile, sc, acc, m, l, c, rowbuf, ones, ptrs);
+    if (route(dev) == RUN)
+        (fused_attention(B, T, H, hs, tile) ? sl_cuda_attention : backend().attention)(qkv, o, L, B, T, H, hs, scale, tile, sc, acc, m, l, c,
+                                                                                     rowbuf, ones, ptrs);
     return 0;
 }
 
@@ -382,7 +398,9 @@ int sl_attention_bwd(int dev, const float* qkv, const float* o, const float* L, 
     float* ones = s.floats(tile > hs ? tile : hs);
     void* ptrs = s.bytes((size_t)(9 * bh) * sizeof(void*));
     if (!s.ok) return kOutOfMemory;
-    if (route(dev) == RUN) backend().attention_bwd(qkv, o, L, dout, dqkv, B, T, H, hs, scale, tile, sc, dp, doc, oc, lrow, dd, rowbuf, ones, ptrs);
+    if (route(dev) == RUN)
+        (fused_attention(B, T, H, hs, tile) ? sl_cuda_attention_bwd : backend().attention_bwd)(qkv, o, L, dout, dqkv, B, T, H, hs, scale, tile,
+                                                                                             sc, dp, doc, oc, lrow, dd, rowbuf, ones, ptrs);
     return 0;
 }
 

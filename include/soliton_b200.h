@@ -139,6 +139,19 @@ void sl_cuda_layernorm(const float* x, const float* w, const float* b, float* y,
 void sl_cuda_layernorm_bwd(const float* dy, const float* x, const float* w, const float* mean, const float* invstd,
                            float* dx, float* dw, float* db, int64_t outer, int64_t c, float* tmp, float* sg, float* sgx,
                            float* ones_c, float* ones_rows);
+/* core/soliton/api.d:51-55 -> core/cuda/kernels.cu:536-692: causal attention over packed qkv (B, T, 3, H, hs) -> out
+ * (B, T, H, hs) and L (B, H, T) = row maximum + log of the softmax denominator; backward writes all of dqkv. Fused
+ * kernels that keep scores and probabilities on chip; products with TF32 operands and fp32 accumulation, so for
+ * callers that enabled TF32 matmuls (sl_set_tf32). Only hs = 64 and T a multiple of 64
+ * (sl_cuda_attention_supported); other shapes set the sticky error 2 and do nothing. Of the reference's scratch
+ * arguments only `oc` is used (backward: B * H * T floats of row dots; the reference sizes it B * H * tile * hs); the
+ * others may be NULL. Results do not vary from run to run: no atomics, one fixed summation order. */
+int sl_cuda_attention_supported(int64_t T, int64_t hs);
+void sl_cuda_attention(const float* qkv, float* out, float* L, int64_t B, int64_t T, int64_t H, int64_t hs, float scale,
+                       int64_t tile, float* s, float* acc, float* m, float* l, float* c, float* rowbuf, float* ones, void* ptrs);
+void sl_cuda_attention_bwd(const float* qkv, const float* out, const float* L, const float* dout, float* dqkv, int64_t B,
+                           int64_t T, int64_t H, int64_t hs, float scale, int64_t tile, float* s, float* dp, float* doc,
+                           float* oc, float* lrow, float* D, float* rowbuf, float* ones, void* ptrs);
 /* No counterpart in the reference; modelled on sl_cuda_set_workspace (core/cuda/kernels.cu:115). A host core that
  * owns the allocator hands the path its workspace (slb_workspace_bytes() bytes from its pool) once per device. */
 int sl_cuda_dp_set_workspace(void* p, size_t n);

@@ -1,0 +1,132 @@
+"""Fused causal attention, forward and backward (csrc/attention_kernels.cu), through the backend-level C ABI, against
+float64 and against the reference's own kernels in TF32 mode (core/cuda/kernels.cu:536-692 with sl_cuda_set_tf32(1),
+built unmodified into oracle/_ref/).
+
+Floating point with TF32 operands (10-bit mantissa): neither implementation is exact, so both are measured against a
+float64 evaluation of the same formulas and the fused kernels must be at least as close as the reference's TF32 path
+is (with a factor 1.5 of slack for the different operand rounding), and inside an absolute bar that follows from the
+operand precision: 2^-10 relative per operand, growing with the square root of the number of products per sum.
+The reference's own test bar for attention (tests/test_ops.py: rtol 1e-3 / atol 1e-4 and 1e-2 / 1e-3 for gradients)
+is an fp32 bar and is not met by its own TF32 path; the table printed on failure shows both."""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+
+from oracle import build as obuild
+from soliton_b200._C import lib
+from tests.gpu_util import DevBuf, check_ok
+
+pytestmark = pytest.mark.gpu
+F, L, P = C.c_float, C.c_int64, C.c_void_p
+HS = 64
+# (B, T, H): T a multiple of 64; 1024 is GPT-2's context, 64 a single tile, 192 an odd number of tiles
+SHAPES = [(1, 64, 1), (2, 192, 3), (1, 256, 2), (2, 1024, 2), (1, 512, 12)]
+
+
+@pytest.fixture(scope="module")
+def ref(cuda):
+    path = obuild.build_ref()
+    if not path or not os.path.exists(path):
+        pytest.skip("reference CUDA backend not built (no reference checkout at build time)")
+    r = C.CDLL(path)
+    assert r.sl_cuda_set_device(0) == 0
+    r.sl_cuda_attention.argtypes = [P] * 3 + [L] * 4 + [F, L] + [P] * 8
+    r.sl_cuda_attention.restype = None
+    r.sl_cuda_attention_bwd.argtypes = [P] * 5 + [L] * 4 + [F, L] + [P] * 9
+    r.sl_cuda_attention_bwd.restype = None
+    r.sl_cuda_set_tf32.argtypes = [C.c_int]
+    r.sl_cuda_set_tf32.restype = None
+    r.sl_cuda_set_tf32(1)
+    yield r
+    r.sl_cuda_set_tf32(0)
+
+
+def truth(qkv, dout, scale):
+    """float64: out, L, dqkv for qkv (B, T, 3, H, hs), dout (B, T, H, hs)."""
+    qkv, dout = qkv.astype(np.float64), dout.astype(np.float64)
+    q, k, v = (qkv[:, :, i].transpose(0, 2, 1, 3) for i in range(3))  # (B, H, T, hs)
+    do = dout.transpose(0, 2, 1, 3)
+    T = q.shape[2]
+    s = scale * q @ k.transpose(0, 1, 3, 2)
+    s = np.where(np.tril(np.ones((T, T), bool)), s, -np.inf)
+    m = s.max(axis=-1, keepdims=True)
+    e = np.exp(s - m)
+    l = e.sum(axis=-1, keepdims=True)
+    p = e / l
+    o = p @ v
+    dv = p.transpose(0, 1, 3, 2) @ do
+    dp = do @ v.transpose(0, 1, 3, 2)
+    ds = p * (dp - (do * o).sum(axis=-1, keepdims=True)) * scale
+    dq, dk = ds @ k, ds.transpose(0, 1, 3, 2) @ q
+    dqkv = np.stack([g.transpose(0, 2, 1, 3) for g in (dq, dk, dv)], axis=2)
+    return o.transpose(0, 2, 1, 3), (m + np.log(l))[..., 0], dqkv
+
+
+def chunks_for(dim):
+    c = 1
+    while c * c < dim:
+        c += 1
+    return c
+
+
+def run(fns, B, T, H, qkv, dout, scale):
+    """Both passes with the scratch the reference's host core hands over (core/soliton/api.d:501-541)."""
+    fwd, bwd = fns
+    tile = 256 if T % 256 == 0 else T
+    bh = B * H
+    rows = bh * tile
+    d = {k: DevBuf(v) for k, v in dict(qkv=qkv, dout=dout).items()}
+    o = {k: DevBuf(n=n) for k, n in dict(out=B * T * H * HS, L=bh * T, dqkv=B * T * 3 * H * HS, s=rows * tile, dp=rows * tile,
+                                         acc=rows * HS, oc=rows * HS, m=rows, l=rows, c=rows, rowbuf=rows * (chunks_for(tile) + 1),
+                                         ones=max(tile, HS), ptrs=2 * 9 * bh).items()}
+    fwd(d["qkv"].ptr, o["out"].ptr, o["L"].ptr, B, T, H, HS, scale, tile, o["s"].ptr, o["acc"].ptr, o["m"].ptr, o["l"].ptr,
+        o["c"].ptr, o["rowbuf"].ptr, o["ones"].ptr, o["ptrs"].ptr)
+    bwd(d["qkv"].ptr, o["out"].ptr, o["L"].ptr, d["dout"].ptr, o["dqkv"].ptr, B, T, H, HS, scale, tile, o["s"].ptr, o["dp"].ptr,
+        o["acc"].ptr, o["oc"].ptr, o["m"].ptr, o["l"].ptr, o["rowbuf"].ptr, o["ones"].ptr, o["ptrs"].ptr)
+    check_ok()
+    return {k: o[k].get() for k in ("out", "L", "dqkv")}
+
+
+@pytest.mark.parametrize("B,T,H", SHAPES)
+def test_attention_forward_and_backward(ref, B, T, H):
+    rng = np.random.default_rng(B * 1000 + T + H)
+    qkv = rng.standard_normal((B, T, 3, H, HS)).astype(np.float32)
+    qkv[:, :, 0] *= 1.5                                               # scores of a few units: a softmax with peaks
+    dout = rng.standard_normal((B, T, H, HS)).astype(np.float32)
+    scale = 1.0 / np.sqrt(HS)
+    ours = run((lib.sl_cuda_attention, lib.sl_cuda_attention_bwd), B, T, H, qkv, dout, scale)
+    again = run((lib.sl_cuda_attention, lib.sl_cuda_attention_bwd), B, T, H, qkv, dout, scale)
+    theirs = run((ref.sl_cuda_attention, ref.sl_cuda_attention_bwd), B, T, H, qkv, dout, scale)
+    assert ref.sl_cuda_check() == 0
+    want = dict(zip(("out", "L", "dqkv"), truth(qkv, dout, scale)))
+    report = []
+    for k in ("out", "L", "dqkv"):
+        np.testing.assert_array_equal(ours[k], again[k])             # no atomics, fixed orders: the same bits every run
+        t = want[k].ravel()
+        mine, ref_err = np.abs(ours[k] - t), np.abs(theirs[k] - t)
+        report.append(f"{k}: ours max {mine.max():.3e} rms {np.sqrt((mine ** 2).mean()):.3e}; "
+                      f"reference max {ref_err.max():.3e} rms {np.sqrt((ref_err ** 2).mean()):.3e}")
+    text = "\n".join(report)
+    for k in ("out", "L", "dqkv"):
+        t = want[k].ravel()
+        mine, ref_err = np.abs(ours[k] - t), np.abs(theirs[k] - t)
+        rms, ref_rms = np.sqrt((mine ** 2).mean()), np.sqrt((ref_err ** 2).mean())
+        assert np.isfinite(ours[k]).all(), text
+        assert rms <= 1.5 * ref_rms + 1e-7, text
+        # 2^-10 per operand, sums of up to T products of magnitude about one, three roundings deep for gradients
+        bar = 2.0 ** -10 * (8 if k == "dqkv" else 4) * max(1.0, float(np.abs(t).max()))
+        assert mine.max() <= bar, text
+
+
+def test_unsupported_shapes_are_refused(cuda):
+    assert lib.sl_cuda_attention_supported(1024, 64) == 1
+    assert lib.sl_cuda_attention_supported(1000, 64) == 0
+    assert lib.sl_cuda_attention_supported(1024, 32) == 0
+    buf = DevBuf(n=4096)
+    lib.sl_cuda_attention(buf.ptr, buf.ptr, buf.ptr, 1, 16, 1, 16, 0.25, 16, None, None, None, None, None, None, None, None)
+    lib.sl_sync(2)
+    assert lib.sl_check(2) == 2                                       # sticky launch error, nothing ran
+    lib.slb_clear_error()
+    assert lib.sl_check(2) == 0
