@@ -77,6 +77,7 @@ def parse():
     ap.add_argument("--fabric", action="store_true", help="NVLink fabric ceiling: copy engines and kernels, one and both directions")
     ap.add_argument("--bare", action="store_true", help="gradient mean only, no optimizer update (link-bound floor)")
     ap.add_argument("--attention", action="store_true", help="fused causal attention against the reference's TF32 path")
+    ap.add_argument("--xent", action="store_true", help="cross entropy forward and backward against the reference's kernels")
     ap.add_argument("--layernorm", action="store_true", help="layer normalisation forward and backward against the reference's kernels")
     return ap.parse_args()
 
@@ -818,6 +819,59 @@ def run_attention(args):
     print(json.dumps({"metric": "attention_ms", "rows": rows_out}), flush=True)
 
 
+def run_xent(args):
+    """Cross entropy forward (including its blocking read of the mean) and backward, this library's kernels and the
+    reference's (core/cuda/kernels.cu:488-534 from oracle/_ref/) on the same buffers: GPT-2's 8,192 rows of 50,257
+    logits (1.65 GB, larger than L2), CUDA events, median of 20. GB/s are algorithmic: 4 bytes per logit forward,
+    8 backward (read the logits, write the gradient)."""
+    import numpy as np
+    import torch
+    from soliton_b200 import tensor as T
+    from soliton_b200._C import lib
+    T._dev(T.CUDA)
+    R = reference_gpu_lib()
+    C = ctypes
+    if R is not None:
+        assert R.sl_cuda_set_device(0) == 0
+        R.sl_cuda_cross_entropy.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]
+        R.sl_cuda_cross_entropy.restype = C.c_double
+        R.sl_cuda_cross_entropy_bwd.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_float]
+    hbm, hbm_kind = hbm_peak()
+
+    def timed(fn, reps=20):
+        out = []
+        for i in range(reps + 3):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            if i >= 3:
+                out.append(e0.elapsed_time(e1))
+        return statistics.median(out)
+
+    rows_out = []
+    for n, v in ((8192, 50257), (8192, 50304)):
+        rng = np.random.default_rng(0)
+        logits = T.tensor(rng.standard_normal((n, v), dtype=np.float32), "cuda")
+        t = T.tensor(rng.integers(0, v, n).astype(np.int32).view(np.float32), "cuda")
+        dl, rowloss = T.empty((n, v), "cuda"), T.empty((n,), "cuda")
+        T.synchronize()
+        for name, Lib in (("this library", lib), ("reference", R)):
+            if Lib is None:
+                continue
+            loss = []
+            fwd = lambda: loss.append(Lib.sl_cuda_cross_entropy(logits.ptr, t.ptr, n, v, rowloss.ptr))  # noqa: E731
+            bwd = lambda: Lib.sl_cuda_cross_entropy_bwd(logits.ptr, t.ptr, dl.ptr, n, v, 1.0)  # noqa: E731
+            tf, tb = timed(fwd), timed(bwd)
+            rows_out.append({"rows": n, "v": v, "by": name, "loss": loss[-1], "fwd_ms": round(tf, 4), "bwd_ms": round(tb, 4),
+                             "fwd_GBps": round(4 * n * v / tf / 1e6, 1), "bwd_GBps": round(8 * n * v / tb / 1e6, 1),
+                             "fwd_frac_of_hbm": round(4 * n * v / tf / 1e6 / hbm, 3), "bwd_frac_of_hbm": round(8 * n * v / tb / 1e6 / hbm, 3)})
+        assert lib.sl_check(T.CUDA) == 0
+    print(json.dumps({"metric": "cross_entropy_algorithmic_GBps", "hbm_peak": hbm, "hbm_peak_kind": hbm_kind, "rows": rows_out}), flush=True)
+
+
 def run_reference_gpu(args, rank, local_rank, world):
     """The reference's own GPU path as an arm of its own (the product arm also carries it as `gpu_baseline`)."""
     import torch
@@ -854,6 +908,8 @@ def main():
         return run_layernorm(args)
     if args.attention:
         return run_attention(args)
+    if args.xent:
+        return run_xent(args)
     if world == 1 and args.gpus > 1:
         # launched without torchrun: start one process per GPU ourselves
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",

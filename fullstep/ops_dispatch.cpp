@@ -203,6 +203,14 @@ bool fused_attention(int64_t B, int64_t T, int64_t H, int64_t hs, int64_t tile) 
     }();
     return g_tf32 && !refused && sl_cuda_attention_supported(T, hs) && B * H * T <= B * H * tile * hs;
 }
+// SOLITON_FULLSTEP_XENT=reference: cross entropy from the reference backend instead of this library's kernels.
+bool reference_xent() {
+    static const bool wanted = [] {
+        const char* v = getenv("SOLITON_FULLSTEP_XENT");
+        return v && strcmp(v, "reference") == 0;
+    }();
+    return wanted;
+}
 }  // namespace
 
 extern "C" {
@@ -353,12 +361,13 @@ double sl_cross_entropy(int dev, const float* logits, const int* t, int64_t n, i
     float* rowloss = s.floats(n);
     *err = s.ok ? 0 : kOutOfMemory;
     if (!s.ok) return NAN;
-    return route(dev) == RUN ? backend().cross_entropy(logits, t, n, v, rowloss) : NAN;
+    if (route(dev) != RUN) return NAN;
+    return reference_xent() ? backend().cross_entropy(logits, t, n, v, rowloss) : sl_cuda_cross_entropy(logits, t, n, v, rowloss);
 }
 
 // api.d:493-499: no scratch
 int sl_cross_entropy_bwd(int dev, const float* logits, const int* t, float* dl, int64_t n, int64_t v, float dloss) {
-    if (route(dev) == RUN) backend().cross_entropy_bwd(logits, t, dl, n, v, dloss);
+    if (route(dev) == RUN) (reference_xent() ? backend().cross_entropy_bwd : sl_cuda_cross_entropy_bwd)(logits, t, dl, n, v, dloss);
     return 0;
 }
 

@@ -152,6 +152,13 @@ void sl_cuda_attention(const float* qkv, float* out, float* L, int64_t B, int64_
 void sl_cuda_attention_bwd(const float* qkv, const float* out, const float* L, const float* dout, float* dqkv, int64_t B,
                            int64_t T, int64_t H, int64_t hs, float scale, int64_t tile, float* s, float* dp, float* doc,
                            float* oc, float* lrow, float* D, float* rowbuf, float* ones, void* ptrs);
+/* core/soliton/api.d:46-47 -> core/cuda/kernels.cu:488-534: cross entropy of n rows of v logits against integer
+ * targets: the mean loss (blocking: the value comes back to the host), and the gradient dl = (softmax - onehot) *
+ * dloss / n. One pass over the logits forward, one read and one write backward. `rowloss` (n floats) is the
+ * reference's scratch; when it is 8-byte aligned the mean is formed on the device in double precision and
+ * overwrites its first 8 bytes. */
+double sl_cuda_cross_entropy(const float* logits, const int* t, int64_t n, int64_t v, float* rowloss);
+void sl_cuda_cross_entropy_bwd(const float* logits, const int* t, float* dl, int64_t n, int64_t v, float dloss);
 /* No counterpart in the reference; modelled on sl_cuda_set_workspace (core/cuda/kernels.cu:115). A host core that
  * owns the allocator hands the path its workspace (slb_workspace_bytes() bytes from its pool) once per device. */
 int sl_cuda_dp_set_workspace(void* p, size_t n);
