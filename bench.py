@@ -756,10 +756,11 @@ def run_layernorm(args):
 
 
 def run_attention(args):
-    """Causal attention, forward and backward, this library's fused kernels and the reference's TF32 path
-    (core/cuda/kernels.cu:536-692 from oracle/_ref/ with sl_cuda_set_tf32(1)) on the same buffers, at GPT-2's shapes
-    (batch 8, context 1024, head size 64; 12 and 16 heads), CUDA events, median of 20. TFLOP/s count the causal half
-    of the products only: forward 2 products, backward 5, each 2 * T * T / 2 * 64 flops per head."""
+    """Causal attention, forward and backward, this library's fused kernels and the reference's path
+    (core/cuda/kernels.cu:536-692 from oracle/_ref/) on the same buffers, in both matmul precisions (fp32, and TF32
+    as after sl_set_tf32(1)), at GPT-2's shapes (batch 8, context 1024, head size 64; 12 and 16 heads), CUDA events,
+    median of 20. TFLOP/s count the causal half of the products only: forward 2 products, backward 5, each
+    2 * T * T / 2 * 64 flops per head."""
     import numpy as np
     import torch
     from soliton_b200 import tensor as T
@@ -772,7 +773,6 @@ def run_attention(args):
         R.sl_cuda_attention.argtypes = [C.c_void_p] * 3 + [C.c_int64] * 4 + [C.c_float, C.c_int64] + [C.c_void_p] * 8
         R.sl_cuda_attention_bwd.argtypes = [C.c_void_p] * 5 + [C.c_int64] * 4 + [C.c_float, C.c_int64] + [C.c_void_p] * 9
         R.sl_cuda_set_tf32.argtypes = [C.c_int]
-        R.sl_cuda_set_tf32(1)
 
     def timed(fn, reps=20):
         out = []
@@ -802,18 +802,22 @@ def run_attention(args):
         rowbuf, ones, ptrs = T.empty((rows, 17), "cuda"), T.empty((tile,), "cuda"), T.empty((18 * bh,), "cuda")
         T.synchronize()
         scale = 0.125
-        for name, Lib in (("this library", lib), ("reference, TF32", R)):
+        for tf32, name, Lib in ((1, "this library", lib), (1, "reference", R), (0, "this library", lib), (0, "reference", R)):
             if Lib is None:
                 continue
+            lib.sl_cuda_attention_set_tf32(tf32)
+            if R is not None:
+                R.sl_cuda_set_tf32(tf32)
             fwd = lambda: Lib.sl_cuda_attention(qkv.ptr, out.ptr, Lb.ptr, B, Tn, H, hs, scale, tile, s.ptr, acc.ptr, m.ptr, l.ptr,  # noqa: E731
                                                 c.ptr, rowbuf.ptr, ones.ptr, ptrs.ptr)
             bwd = lambda: Lib.sl_cuda_attention_bwd(qkv.ptr, out.ptr, Lb.ptr, dout.ptr, dqkv.ptr, B, Tn, H, hs, scale, tile, s.ptr,  # noqa: E731
                                                     dp.ptr, acc.ptr, oc.ptr, m.ptr, l.ptr, rowbuf.ptr, ones.ptr, ptrs.ptr)
             tf, tb = timed(fwd), timed(bwd)
             flop = bh * Tn * Tn * hs  # one causal product: 2 * T * T / 2 * hs per head
-            rows_out.append({"B": B, "T": Tn, "H": H, "by": name, "fwd_ms": round(tf, 4), "bwd_ms": round(tb, 4),
+            rows_out.append({"B": B, "T": Tn, "H": H, "precision": "tf32" if tf32 else "fp32", "by": name, "fwd_ms": round(tf, 4), "bwd_ms": round(tb, 4),
                              "fwd_causal_TFLOPs": round(2 * flop / tf / 1e9, 1), "bwd_causal_TFLOPs": round(5 * flop / tb / 1e9, 1)})
         assert lib.sl_check(T.CUDA) == 0
+    lib.sl_cuda_attention_set_tf32(0)
     if R is not None:
         R.sl_cuda_set_tf32(0)
     print(json.dumps({"metric": "attention_ms", "rows": rows_out}), flush=True)

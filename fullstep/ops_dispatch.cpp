@@ -192,16 +192,14 @@ int64_t chunks_for(int64_t dim) {  // api.d:113-119: about sqrt(dim) chunks for 
 size_t sort_temp_bytes(int64_t n) { return (size_t)n * 16 + (size_t(1) << 20); }  // api.d:124-127
 int64_t attention_tile(int64_t T) { return T % 256 == 0 ? 256 : T; }             // core/cuda/kernels.cu:612
 
-// Whether matmuls run with TF32 operands (sl_set_tf32). Attention goes to this library's fused kernels only then:
-// they multiply in TF32, which is the arithmetic the caller asked for in that mode and not otherwise.
-bool g_tf32 = false;
-// SOLITON_FULLSTEP_ATTN=reference: attention from the reference backend in every mode.
+// SOLITON_FULLSTEP_ATTN=reference: attention from the reference backend instead of this library's fused kernels
+// (which follow sl_set_tf32 like the reference's: fp32-class products by default, TF32 ones when enabled).
 bool fused_attention(int64_t B, int64_t T, int64_t H, int64_t hs, int64_t tile) {
     static const bool refused = [] {
         const char* v = getenv("SOLITON_FULLSTEP_ATTN");
         return v && strcmp(v, "reference") == 0;
     }();
-    return g_tf32 && !refused && sl_cuda_attention_supported(T, hs) && B * H * T <= B * H * tile * hs;
+    return !refused && sl_cuda_attention_supported(T, hs) && B * H * T <= B * H * tile * hs;
 }
 // SOLITON_FULLSTEP_XENT=reference: cross entropy from the reference backend instead of this library's kernels.
 bool reference_xent() {
@@ -219,7 +217,7 @@ extern "C" {
 void sl_set_tf32(int dev, int on) {
     if (route(dev) == RUN) {
         backend().set_tf32(on);
-        g_tf32 = on != 0;
+        sl_cuda_attention_set_tf32(on);
     }
 }
 

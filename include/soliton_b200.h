@@ -141,11 +141,14 @@ void sl_cuda_layernorm_bwd(const float* dy, const float* x, const float* w, cons
                            float* ones_c, float* ones_rows);
 /* core/soliton/api.d:51-55 -> core/cuda/kernels.cu:536-692: causal attention over packed qkv (B, T, 3, H, hs) -> out
  * (B, T, H, hs) and L (B, H, T) = row maximum + log of the softmax denominator; backward writes all of dqkv. Fused
- * kernels that keep scores and probabilities on chip; products with TF32 operands and fp32 accumulation, so for
- * callers that enabled TF32 matmuls (sl_set_tf32). Only hs = 64 and T a multiple of 64
+ * kernels that keep scores and probabilities on chip; products on the tensor cores with fp32 accumulation. Like the
+ * reference's matmuls they have two precisions: fp32-class by default (every operand split into two TF32 pieces,
+ * three products each), plain TF32 operands after sl_cuda_attention_set_tf32(1) -- call it wherever
+ * sl_cuda_set_tf32 (core/cuda/kernels.cu:117-122) is called. Only hs = 64 and T a multiple of 64
  * (sl_cuda_attention_supported); other shapes set the sticky error 2 and do nothing. Of the reference's scratch
  * arguments only `oc` is used (backward: B * H * T floats of row dots; the reference sizes it B * H * tile * hs); the
  * others may be NULL. Results do not vary from run to run: no atomics, one fixed summation order. */
+void sl_cuda_attention_set_tf32(int on);
 int sl_cuda_attention_supported(int64_t T, int64_t hs);
 void sl_cuda_attention(const float* qkv, float* out, float* L, int64_t B, int64_t T, int64_t H, int64_t hs, float scale,
                        int64_t tile, float* s, float* acc, float* m, float* l, float* c, float* rowbuf, float* ones, void* ptrs);

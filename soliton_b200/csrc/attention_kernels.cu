@@ -29,11 +29,9 @@ constexpr int S_NK = 68;     // row stride of a tile read as B[k][n] = tile[n][k
 constexpr int S_KN = 72;     // row stride of a tile read as B[k][n] = tile[k][n]: lanes (k = t, n = g) hit 32 banks
 constexpr int S_P = 68;      // per-warp staging of a 16 x 64 probability block, read back as an A operand
 
-__device__ __forceinline__ uint32_t tf32(float x) {
-    uint32_t r;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-    return r;
-}
+// Round to TF32 (10 mantissa bits), nearest with ties away from zero like cvt.rna.tf32.f32, in two integer
+// operations: half a TF32 unit is added to the magnitude and the 13 low bits are cleared.
+__device__ __forceinline__ uint32_t tf32(float x) { return (__float_as_uint(x) + 0x1000u) & 0xffffe000u; }
 // D(16x8) += A(16x8, row) * B(8x8, col). Lane l: g = l / 4, t = l % 4. A: a0 (g, t) a1 (g+8, t) a2 (g, t+4) a3 (g+8, t+4);
 // B: b0 (k = t, n = g) b1 (k = t+4, n = g); D: d0 (g, 2t) d1 (g, 2t+1) d2 (g+8, 2t) d3 (g+8, 2t+1).
 __device__ __forceinline__ void mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -41,6 +39,12 @@ __device__ __forceinline__ void mma(float (&d)[4], const uint32_t (&a)[4], uint3
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ float ex2(float x) {  // 2^x, flushing; ex2(-inf) = 0
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+constexpr float kLog2e = 1.4426950408889634f;
 __device__ __forceinline__ float quad_max(float v) {
     v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
     return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
@@ -50,13 +54,51 @@ __device__ __forceinline__ float quad_sum(float v) {
     return v + __shfl_xor_sync(0xffffffffu, v, 2);
 }
 
-// A 64 x 64 tile of one head (rows row0 .., row stride ld floats) into shared memory as TF32, row stride `stride`.
-__device__ __forceinline__ void load_tile(float* dst, int stride, const float* src, int64_t ld, int row0) {
-    for (int i = threadIdx.x; i < BT * (HS / 4); i += kThreads) {
-        const int r = i >> 4, c = (i & 15) * 4;
-        const float4 v = *reinterpret_cast<const float4*>(src + (int64_t)(row0 + r) * ld + c);
-        uint32_t* d = reinterpret_cast<uint32_t*>(dst + r * stride + c);
-        d[0] = tf32(v.x), d[1] = tf32(v.y), d[2] = tf32(v.z), d[3] = tf32(v.w);
+// One operand in the two pieces of the split-precision products: x = hi + lo to about 2^-22, both TF32.
+__device__ __forceinline__ void split(float x, uint32_t& hi, uint32_t& lo) {
+    hi = tf32(x);
+    lo = tf32(x - __uint_as_float(hi));
+}
+
+// A 64 x 64 tile of one head (rows row0 .., row stride ld floats) into shared memory with row stride `stride`:
+// rounded to TF32, or as it is when the products are split (X3). All eight 128-bit loads of a thread are issued
+// before the first store, so that they are in flight together.
+template <bool X3>
+__device__ __forceinline__ void load_tile(float* dst, int stride, const float* __restrict__ src, int64_t ld, int row0) {
+    constexpr int kPer = BT * (HS / 4) / kThreads;  // 8
+    float4 v[kPer];
+#pragma unroll
+    for (int u = 0; u < kPer; u++) {
+        const int i = threadIdx.x + u * kThreads;
+        v[u] = __ldg(reinterpret_cast<const float4*>(src + (int64_t)(row0 + (i >> 4)) * ld + (i & 15) * 4));
+    }
+#pragma unroll
+    for (int u = 0; u < kPer; u++) {
+        const int i = threadIdx.x + u * kThreads;
+        float* d = dst + (i >> 4) * stride + (i & 15) * 4;
+        if constexpr (X3) *reinterpret_cast<float4*>(d) = v[u];
+        else *reinterpret_cast<uint4*>(d) = make_uint4(tf32(v[u].x), tf32(v[u].y), tf32(v[u].z), tf32(v[u].w));
+    }
+}
+// The same tile into two places with two strides: a tile that is read both as B[k][n] = tile[n][k] and as
+// B[k][n] = tile[k][n] has no single stride that keeps both reads free of bank conflicts.
+template <bool X3>
+__device__ __forceinline__ void load_tile2(float* dst, int stride, float* dst2, int stride2, const float* __restrict__ src,
+                                           int64_t ld, int row0) {
+    constexpr int kPer = BT * (HS / 4) / kThreads;  // 8
+    float4 v[kPer];
+#pragma unroll
+    for (int u = 0; u < kPer; u++) {
+        const int i = threadIdx.x + u * kThreads;
+        v[u] = __ldg(reinterpret_cast<const float4*>(src + (int64_t)(row0 + (i >> 4)) * ld + (i & 15) * 4));
+    }
+#pragma unroll
+    for (int u = 0; u < kPer; u++) {
+        const int i = threadIdx.x + u * kThreads;
+        float4 w = v[u];
+        if constexpr (!X3) w = make_float4(__uint_as_float(tf32(w.x)), __uint_as_float(tf32(w.y)), __uint_as_float(tf32(w.z)), __uint_as_float(tf32(w.w)));
+        *reinterpret_cast<float4*>(dst + (i >> 4) * stride + (i & 15) * 4) = w;
+        *reinterpret_cast<float4*>(dst2 + (i >> 4) * stride2 + (i & 15) * 4) = w;
     }
 }
 // The A operand of 16 rows (row0 + g, row0 + g + 8) x 64 columns straight from memory: 8 k-steps of 8 columns.
@@ -69,48 +111,88 @@ __device__ __forceinline__ void load_a(uint32_t (&a)[8][4], const float* src, in
         a[ks][2] = tf32(r0[ks * 8 + t + 4]), a[ks][3] = tf32(r1[ks * 8 + t + 4]);
     }
 }
-// acc(16 x 64) += A(16 x 64 in registers) * tile^T, tile (64 x 64) in shared memory with row stride S_NK:
-// acc[nt] column n = nt * 8 + .., B[k][n] = tile[n][k].
-__device__ __forceinline__ void mma_a_tileT(float (&acc)[8][4], const uint32_t (&a)[8][4], const float* tile, int g, int t) {
+// The B operand of k-step ks and column block nt out of a 64 x 64 tile in shared memory with row stride sb:
+// TRANS ? B[k][n] = tile[n][k] : B[k][n] = tile[k][n].
+template <bool TRANS>
+__device__ __forceinline__ void b_index(int ks, int nt, int sb, int g, int t, int& i0, int& i1) {
+    if constexpr (TRANS) i0 = (nt * 8 + g) * sb + ks * 8 + t, i1 = i0 + 4;
+    else i0 = (ks * 8 + t) * sb + nt * 8 + g, i1 = i0 + 4 * sb;
+}
+// acc(16 x 64) += A * B, A (16 x 64) in registers as TF32, B from a tile of TF32 values.
+template <bool TRANS>
+__device__ __forceinline__ void gemm_ra(float (&acc)[8][4], const uint32_t (&a)[8][4], const float* tile, int sb, int g, int t) {
     const uint32_t* u = reinterpret_cast<const uint32_t*>(tile);
 #pragma unroll
     for (int ks = 0; ks < 8; ks++)
 #pragma unroll
-        for (int nt = 0; nt < 8; nt++) mma(acc[nt], a[ks], u[(nt * 8 + g) * S_NK + ks * 8 + t], u[(nt * 8 + g) * S_NK + ks * 8 + t + 4]);
+        for (int nt = 0; nt < 8; nt++) {
+            int i0, i1;
+            b_index<TRANS>(ks, nt, sb, g, t, i0, i1);
+            mma(acc[nt], a[ks], u[i0], u[i1]);
+        }
 }
-// acc(16 x 64) += P(16 x 64, staged in this warp's shared memory, stride S_P) * tile, tile (64 x 64) with row stride
-// `stride`: B[k][n] = tile[k][n].
-__device__ __forceinline__ void mma_p_tile(float (&acc)[8][4], const float* p, const float* tile, int stride, int g, int t) {
-    const uint32_t* up = reinterpret_cast<const uint32_t*>(p);
-    const uint32_t* u = reinterpret_cast<const uint32_t*>(tile);
+// acc(16 x 64) += A * B, A (rows g and g + 8 of `a`, row stride sa) and B both from shared memory. Without X3 both
+// hold TF32 values: one product. With X3 both hold fp32 values, split as they are read: lo x hi + hi x lo + hi x hi,
+// smallest terms first -- an fp32-class product out of three TF32 ones.
+template <bool X3, bool TRANS>
+__device__ __forceinline__ void gemm_sa(float (&acc)[8][4], const float* a, int sa, const float* tile, int sb, int g, int t) {
 #pragma unroll
     for (int ks = 0; ks < 8; ks++) {
-        uint32_t a[4];
-        a[0] = up[g * S_P + ks * 8 + t], a[1] = up[(g + 8) * S_P + ks * 8 + t];
-        a[2] = up[g * S_P + ks * 8 + t + 4], a[3] = up[(g + 8) * S_P + ks * 8 + t + 4];
+        const float a0 = a[g * sa + ks * 8 + t], a1 = a[(g + 8) * sa + ks * 8 + t];
+        const float a2 = a[g * sa + ks * 8 + t + 4], a3 = a[(g + 8) * sa + ks * 8 + t + 4];
+        uint32_t ah[4], al[4];
+        if constexpr (X3) {
+            split(a0, ah[0], al[0]), split(a1, ah[1], al[1]), split(a2, ah[2], al[2]), split(a3, ah[3], al[3]);
+        } else {
+            ah[0] = __float_as_uint(a0), ah[1] = __float_as_uint(a1), ah[2] = __float_as_uint(a2), ah[3] = __float_as_uint(a3);
+        }
 #pragma unroll
-        for (int nt = 0; nt < 8; nt++) mma(acc[nt], a, u[(ks * 8 + t) * stride + nt * 8 + g], u[(ks * 8 + t + 4) * stride + nt * 8 + g]);
+        for (int nt = 0; nt < 8; nt++) {
+            int i0, i1;
+            b_index<TRANS>(ks, nt, sb, g, t, i0, i1);
+            if constexpr (X3) {
+                uint32_t h0, l0, h1, l1;
+                split(tile[i0], h0, l0), split(tile[i1], h1, l1);
+                mma(acc[nt], al, h0, h1);
+                mma(acc[nt], ah, l0, l1);
+                mma(acc[nt], ah, h0, h1);
+            } else {
+                mma(acc[nt], ah, __float_as_uint(tile[i0]), __float_as_uint(tile[i1]));
+            }
+        }
     }
 }
-// A 16 x 64 block in accumulator layout into this warp's staging area, as TF32.
+// A 16 x 64 block in accumulator layout into this warp's staging area: as TF32, or as it is for split products.
+template <bool X3>
 __device__ __forceinline__ void stage(float* p, const float (&v)[8][4], int g, int t) {
-    uint32_t* u = reinterpret_cast<uint32_t*>(p);
 #pragma unroll
     for (int nt = 0; nt < 8; nt++) {
-        u[g * S_P + nt * 8 + 2 * t] = tf32(v[nt][0]), u[g * S_P + nt * 8 + 2 * t + 1] = tf32(v[nt][1]);
-        u[(g + 8) * S_P + nt * 8 + 2 * t] = tf32(v[nt][2]), u[(g + 8) * S_P + nt * 8 + 2 * t + 1] = tf32(v[nt][3]);
+        float2 lo = make_float2(v[nt][0], v[nt][1]), hi = make_float2(v[nt][2], v[nt][3]);
+        if constexpr (!X3) {
+            lo = make_float2(__uint_as_float(tf32(lo.x)), __uint_as_float(tf32(lo.y)));
+            hi = make_float2(__uint_as_float(tf32(hi.x)), __uint_as_float(tf32(hi.y)));
+        }
+        *reinterpret_cast<float2*>(p + g * S_P + nt * 8 + 2 * t) = lo;
+        *reinterpret_cast<float2*>(p + (g + 8) * S_P + nt * 8 + 2 * t) = hi;
     }
+}
+__device__ __forceinline__ void zero(float (&v)[8][4]) {
+#pragma unroll
+    for (int nt = 0; nt < 8; nt++) v[nt][0] = v[nt][1] = v[nt][2] = v[nt][3] = 0;
 }
 
 // ---------------------------------------------------------------- forward
 
-// grid (T / 64, B * H). out = softmax(scale * Q K^T, causal) V; L = row max + log(row sum).
+// grid (T / 64, B * H). out = softmax(scale * Q K^T, causal) V; L = scale * row max + log(row sum).
+// X3: fp32-class products (operands split in two TF32 pieces); otherwise plain TF32 products.
+template <bool X3>
 __global__ void __launch_bounds__(kThreads) k_attn_fwd(const float* __restrict__ qkv, float* __restrict__ out,
                                                        float* __restrict__ L, int T, int H, float scale) {
     extern __shared__ float smem[];
     float* sK = smem;
     float* sV = sK + BT * S_NK;
     float* sP = sV + BT * S_KN;
+    float* sQ = sP + 4 * 16 * S_P;              // X3 only: the block's queries, unrounded
     const int qt = gridDim.x - 1 - blockIdx.x;  // the long rows of the causal triangle first
     const int bh = blockIdx.y, b = bh / H, h = bh % H;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -121,49 +203,56 @@ __global__ void __launch_bounds__(kThreads) k_attn_fwd(const float* __restrict__
     const int row0 = qt * BT + warp * 16;
     float* myP = sP + warp * 16 * S_P;
 
-    uint32_t qa[8][4];
-    load_a(qa, q, ld, row0, g, t);
+    uint32_t qa[X3 ? 1 : 8][4];
+    if constexpr (X3) load_tile<true>(sQ, S_NK, q, ld, qt * BT);  // visible after the barriers of the first tile
+    else load_a(qa, q, ld, row0, g, t);
     float o[8][4];
-#pragma unroll
-    for (int nt = 0; nt < 8; nt++) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0;
-    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0, l1 = 0;
+    zero(o);
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0, l1 = 0;  // maxima of the unscaled products
+    const float sl2 = scale * kLog2e;
 
     for (int j = 0; j <= qt; j++) {
         __syncthreads();  // every warp is done with the previous tile
-        load_tile(sK, S_NK, k, ld, j * BT);
-        load_tile(sV, S_KN, v, ld, j * BT);
+        load_tile<X3>(sK, S_NK, k, ld, j * BT);
+        load_tile<X3>(sV, S_KN, v, ld, j * BT);
         __syncthreads();
         float s[8][4];
+        zero(s);
+        if constexpr (X3) gemm_sa<true, true>(s, sQ + warp * 16 * S_NK, S_NK, sK, S_NK, g, t);
+        else gemm_ra<true>(s, qa, sK, S_NK, g, t);
+        if (j == qt) {  // the diagonal tile: keys after the query are masked
 #pragma unroll
-        for (int nt = 0; nt < 8; nt++) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0;
-        mma_a_tileT(s, qa, sK, g, t);
+            for (int nt = 0; nt < 8; nt++)
+#pragma unroll
+                for (int e = 0; e < 4; e++)
+                    if (nt * 8 + 2 * t + (e & 1) > warp * 16 + g + (e >> 1) * 8) s[nt][e] = -INFINITY;
+        }
+        // running maxima of the raw products; scale > 0 is folded into the exponent: exp(scale * (s - m)) = 2^(sl2 * s - sl2 * m)
         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-        for (int nt = 0; nt < 8; nt++)
-#pragma unroll
-            for (int e = 0; e < 4; e++) {
-                const int col = j * BT + nt * 8 + 2 * t + (e & 1), row = row0 + g + (e >> 1) * 8;
-                float x = s[nt][e] * scale;
-                if (j == qt && col > row) x = -INFINITY;
-                s[nt][e] = x;
-                if (e < 2) mx0 = fmaxf(mx0, x); else mx1 = fmaxf(mx1, x);
-            }
+        for (int nt = 0; nt < 8; nt++) mx0 = fmaxf(mx0, fmaxf(s[nt][0], s[nt][1])), mx1 = fmaxf(mx1, fmaxf(s[nt][2], s[nt][3]));
         mx0 = quad_max(mx0), mx1 = quad_max(mx1);
         const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);  // finite: every row sees its own column at the latest
-        const float c0 = m0 == -INFINITY ? 0.0f : __expf(m0 - n0), c1 = m1 == -INFINITY ? 0.0f : __expf(m1 - n1);
+        const float c0 = ex2((m0 - n0) * sl2), c1 = ex2((m1 - n1) * sl2);  // 0 the first time (m = -inf)
+        const float b0 = n0 * sl2, b1 = n1 * sl2;
         m0 = n0, m1 = n1;
         float r0 = 0, r1 = 0;
 #pragma unroll
         for (int nt = 0; nt < 8; nt++) {
-            s[nt][0] = __expf(s[nt][0] - n0), s[nt][1] = __expf(s[nt][1] - n0);
-            s[nt][2] = __expf(s[nt][2] - n1), s[nt][3] = __expf(s[nt][3] - n1);
+            if constexpr (X3) {  // the difference first: exact for the entries near the maximum, which carry the sum
+                s[nt][0] = ex2((s[nt][0] - n0) * sl2), s[nt][1] = ex2((s[nt][1] - n0) * sl2);
+                s[nt][2] = ex2((s[nt][2] - n1) * sl2), s[nt][3] = ex2((s[nt][3] - n1) * sl2);
+            } else {
+                s[nt][0] = ex2(__fmaf_rn(s[nt][0], sl2, -b0)), s[nt][1] = ex2(__fmaf_rn(s[nt][1], sl2, -b0));
+                s[nt][2] = ex2(__fmaf_rn(s[nt][2], sl2, -b1)), s[nt][3] = ex2(__fmaf_rn(s[nt][3], sl2, -b1));
+            }
             r0 += s[nt][0] + s[nt][1], r1 += s[nt][2] + s[nt][3];
             o[nt][0] *= c0, o[nt][1] *= c0, o[nt][2] *= c1, o[nt][3] *= c1;
         }
         l0 = l0 * c0 + r0, l1 = l1 * c1 + r1;  // per-lane part of the row sum; the four lanes of a row meet at the end
-        stage(myP, s, g, t);
+        stage<X3>(myP, s, g, t);
         __syncwarp();
-        mma_p_tile(o, myP, sV, S_KN, g, t);
+        gemm_sa<X3, false>(o, myP, S_P, sV, S_KN, g, t);
         __syncwarp();
     }
     l0 = quad_sum(l0), l1 = quad_sum(l1);
@@ -176,8 +265,8 @@ __global__ void __launch_bounds__(kThreads) k_attn_fwd(const float* __restrict__
         *reinterpret_cast<float2*>(o1 + nt * 8 + 2 * t) = make_float2(o[nt][2] * i1, o[nt][3] * i1);
     }
     if (t == 0) {
-        L[(int64_t)bh * T + row0 + g] = m0 + logf(l0);
-        L[(int64_t)bh * T + row0 + g + 8] = m1 + logf(l1);
+        L[(int64_t)bh * T + row0 + g] = m0 * scale + logf(l0);
+        L[(int64_t)bh * T + row0 + g + 8] = m1 * scale + logf(l1);
     }
 }
 
@@ -201,13 +290,20 @@ __global__ void __launch_bounds__(kThreads) k_attn_rowdot(const float* __restric
 }
 
 // grid (T / 64, B * H): dQ of 64 query rows, key tiles 0 .. own. P = exp(scale S - L); dS = P (dP - D) scale.
+template <bool X3>
 __global__ void __launch_bounds__(kThreads) k_attn_bwd_dq(const float* __restrict__ qkv, const float* __restrict__ dout,
                                                           const float* __restrict__ L, const float* __restrict__ D,
                                                           float* __restrict__ dqkv, int T, int H, float scale) {
     extern __shared__ float smem[];
-    float* sK = smem;               // stride S_NK: conflict-free for S = Q K^T; two-way conflicts for dQ += dS K
-    float* sV = sK + BT * S_NK;     // stride S_NK: dP = dO V^T
-    float* sP = sV + BT * S_NK;
+    float* sK = smem;               // stride S_NK: read as K^T for S = Q K^T
+    float* sV = sK + BT * S_NK;     // stride S_NK: read as V^T for dP = dO V^T
+    // TF32: the same keys again with stride S_KN, read as K for dQ += dS K free of bank conflicts. The split-product
+    // kernel is bound by its products and short of shared memory: it reads sK both ways.
+    float* sK2 = X3 ? sK : sV + BT * S_NK;
+    constexpr int S_K2 = X3 ? S_NK : S_KN;
+    float* sP = sV + BT * S_NK + (X3 ? 0 : BT * S_KN);
+    float* sQ = sP + 4 * 16 * S_P;  // X3 only: the block's queries and output gradients, unrounded
+    float* sO = sQ + BT * S_NK;
     const int qt = gridDim.x - 1 - blockIdx.x;
     const int bh = blockIdx.y, b = bh / H, h = bh % H;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -219,36 +315,53 @@ __global__ void __launch_bounds__(kThreads) k_attn_bwd_dq(const float* __restric
     const int row0 = qt * BT + warp * 16;
     float* myP = sP + warp * 16 * S_P;
 
-    uint32_t qa[8][4], da[8][4];
-    load_a(qa, q, ld, row0, g, t);
-    load_a(da, dO, ldo, row0, g, t);
-    const float L0 = L[(int64_t)bh * T + row0 + g], L1 = L[(int64_t)bh * T + row0 + g + 8];
+    uint32_t qa[X3 ? 1 : 8][4], da[X3 ? 1 : 8][4];
+    if constexpr (X3) {
+        load_tile<true>(sQ, S_NK, q, ld, qt * BT);  // visible after the barriers of the first tile
+        load_tile<true>(sO, S_NK, dO, ldo, qt * BT);
+    } else {
+        load_a(qa, q, ld, row0, g, t);
+        load_a(da, dO, ldo, row0, g, t);
+    }
+    const float sl2 = scale * kLog2e;  // exp(scale * s - L) = 2^(sl2 * s - log2(e) * L)
+    const float L0 = L[(int64_t)bh * T + row0 + g] * kLog2e, L1 = L[(int64_t)bh * T + row0 + g + 8] * kLog2e;
     const float D0 = D[(int64_t)bh * T + row0 + g], D1 = D[(int64_t)bh * T + row0 + g + 8];
     float dq[8][4];
-#pragma unroll
-    for (int nt = 0; nt < 8; nt++) dq[nt][0] = dq[nt][1] = dq[nt][2] = dq[nt][3] = 0;
+    zero(dq);
 
     for (int j = 0; j <= qt; j++) {
         __syncthreads();
-        load_tile(sK, S_NK, k, ld, j * BT);
-        load_tile(sV, S_NK, v, ld, j * BT);
+        if constexpr (X3) load_tile<true>(sK, S_NK, k, ld, j * BT);
+        else load_tile2<false>(sK, S_NK, sK2, S_KN, k, ld, j * BT);
+        load_tile<X3>(sV, S_NK, v, ld, j * BT);
         __syncthreads();
         float s[8][4], dp[8][4];
-#pragma unroll
-        for (int nt = 0; nt < 8; nt++) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = dp[nt][0] = dp[nt][1] = dp[nt][2] = dp[nt][3] = 0;
-        mma_a_tileT(s, qa, sK, g, t);
-        mma_a_tileT(dp, da, sV, g, t);
+        zero(s), zero(dp);
+        if constexpr (X3) {
+            gemm_sa<true, true>(s, sQ + warp * 16 * S_NK, S_NK, sK, S_NK, g, t);
+            gemm_sa<true, true>(dp, sO + warp * 16 * S_NK, S_NK, sV, S_NK, g, t);
+        } else {
+            gemm_ra<true>(s, qa, sK, S_NK, g, t);
+            gemm_ra<true>(dp, da, sV, S_NK, g, t);
+        }
 #pragma unroll
         for (int nt = 0; nt < 8; nt++)
 #pragma unroll
-            for (int e = 0; e < 4; e++) {
-                const int col = j * BT + nt * 8 + 2 * t + (e & 1), row = row0 + g + (e >> 1) * 8;
-                const float p = (j == qt && col > row) ? 0.0f : __expf(s[nt][e] * scale - (e < 2 ? L0 : L1));
-                s[nt][e] = p * (dp[nt][e] - (e < 2 ? D0 : D1)) * scale;  // dS
-            }
-        stage(myP, s, g, t);
+            for (int e = 0; e < 4; e++) s[nt][e] = ex2(__fmaf_rn(s[nt][e], sl2, -(e < 2 ? L0 : L1)));  // P
+        if (j == qt) {  // the diagonal tile: keys after the query have probability 0
+#pragma unroll
+            for (int nt = 0; nt < 8; nt++)
+#pragma unroll
+                for (int e = 0; e < 4; e++)
+                    if (nt * 8 + 2 * t + (e & 1) > warp * 16 + g + (e >> 1) * 8) s[nt][e] = 0.0f;
+        }
+#pragma unroll
+        for (int nt = 0; nt < 8; nt++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) s[nt][e] = s[nt][e] * (dp[nt][e] - (e < 2 ? D0 : D1)) * scale;  // dS
+        stage<X3>(myP, s, g, t);
         __syncwarp();
-        mma_p_tile(dq, myP, sK, S_NK, g, t);
+        gemm_sa<X3, false>(dq, myP, S_P, sK2, S_K2, g, t);
         __syncwarp();
     }
     float* g0 = dqkv + (int64_t)(b * T + row0 + g) * ld + h * HS;
@@ -263,15 +376,23 @@ __global__ void __launch_bounds__(kThreads) k_attn_bwd_dq(const float* __restric
 // grid (T / 64, B * H): dK and dV of 64 key rows, query tiles own .. last. Works on the transposed problem: rows are
 // keys, columns queries. P^T = exp(scale K Q^T - L[q]); dV += P^T dO; dP^T = V dO^T; dS^T = P^T (dP^T - D[q]) scale;
 // dK += dS^T Q.
+template <bool X3>
 __global__ void __launch_bounds__(kThreads) k_attn_bwd_dkv(const float* __restrict__ qkv, const float* __restrict__ dout,
                                                            const float* __restrict__ L, const float* __restrict__ D,
                                                            float* __restrict__ dqkv, int T, int H, float scale) {
     extern __shared__ float smem[];
-    float* sQ = smem;               // stride S_NK: conflict-free as Q^T (S^T = K Q^T); two-way conflicts for dK += dS^T Q
-    float* sO = sQ + BT * S_NK;     // dO, likewise: dP^T = V dO^T, dV += P^T dO
-    float* sP = sO + BT * S_NK;
+    float* sQ = smem;               // stride S_NK: read as Q^T for S^T = K Q^T
+    float* sO = sQ + BT * S_NK;     // dO, stride S_NK: read as dO^T for dP^T = V dO^T
+    // TF32: the same two tiles again with stride S_KN, read as Q for dK += dS^T Q and as dO for dV += P^T dO free of
+    // bank conflicts. The split-product kernel is bound by its products and short of shared memory: one copy, both ways.
+    float* sQ2 = X3 ? sQ : sO + BT * S_NK;
+    float* sO2 = X3 ? sO : sQ2 + BT * S_KN;
+    constexpr int S_2 = X3 ? S_NK : S_KN;
+    float* sP = sO + BT * S_NK + (X3 ? 0 : 2 * BT * S_KN);
     float* sL = sP + 4 * 16 * S_P;  // L and D of the 64 queries of the tile
     float* sD = sL + BT;
+    float* sK = sD + BT;            // X3 only: the block's keys and values, unrounded
+    float* sV = sK + BT * S_NK;
     const int kt = blockIdx.x;      // key tile 0 has the most query tiles: blocks are issued in that order
     const int bh = blockIdx.y, b = bh / H, h = bh % H;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -283,45 +404,64 @@ __global__ void __launch_bounds__(kThreads) k_attn_bwd_dkv(const float* __restri
     const int row0 = kt * BT + warp * 16;  // key rows of this warp
     float* myP = sP + warp * 16 * S_P;
 
-    uint32_t ka[8][4], va[8][4];
-    load_a(ka, k, ld, row0, g, t);
-    load_a(va, v, ld, row0, g, t);
+    const float sl2 = scale * kLog2e;
+    uint32_t ka[X3 ? 1 : 8][4], va[X3 ? 1 : 8][4];
+    if constexpr (X3) {
+        load_tile<true>(sK, S_NK, k, ld, kt * BT);  // visible after the barriers of the first tile
+        load_tile<true>(sV, S_NK, v, ld, kt * BT);
+    } else {
+        load_a(ka, k, ld, row0, g, t);
+        load_a(va, v, ld, row0, g, t);
+    }
     float dk[8][4], dv[8][4];
-#pragma unroll
-    for (int nt = 0; nt < 8; nt++) dk[nt][0] = dk[nt][1] = dk[nt][2] = dk[nt][3] = dv[nt][0] = dv[nt][1] = dv[nt][2] = dv[nt][3] = 0;
+    zero(dk), zero(dv);
 
     const int tiles = T / BT;
     for (int i = kt; i < tiles; i++) {
         __syncthreads();
-        load_tile(sQ, S_NK, q, ld, i * BT);
-        load_tile(sO, S_NK, dO, ldo, i * BT);
+        if constexpr (X3) {
+            load_tile<true>(sQ, S_NK, q, ld, i * BT);
+            load_tile<true>(sO, S_NK, dO, ldo, i * BT);
+        } else {
+            load_tile2<false>(sQ, S_NK, sQ2, S_KN, q, ld, i * BT);
+            load_tile2<false>(sO, S_NK, sO2, S_KN, dO, ldo, i * BT);
+        }
         if (threadIdx.x < BT) {
-            sL[threadIdx.x] = L[(int64_t)bh * T + i * BT + threadIdx.x];
+            sL[threadIdx.x] = L[(int64_t)bh * T + i * BT + threadIdx.x] * kLog2e;
             sD[threadIdx.x] = D[(int64_t)bh * T + i * BT + threadIdx.x];
         }
         __syncthreads();
         float s[8][4], dp[8][4];
-#pragma unroll
-        for (int nt = 0; nt < 8; nt++) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = dp[nt][0] = dp[nt][1] = dp[nt][2] = dp[nt][3] = 0;
-        mma_a_tileT(s, ka, sQ, g, t);    // S^T: rows keys, columns queries
-        mma_a_tileT(dp, va, sO, g, t);   // dP^T
+        zero(s), zero(dp);
+        if constexpr (X3) {
+            gemm_sa<true, true>(s, sK + warp * 16 * S_NK, S_NK, sQ, S_NK, g, t);    // S^T: rows keys, columns queries
+            gemm_sa<true, true>(dp, sV + warp * 16 * S_NK, S_NK, sO, S_NK, g, t);   // dP^T
+        } else {
+            gemm_ra<true>(s, ka, sQ, S_NK, g, t);
+            gemm_ra<true>(dp, va, sO, S_NK, g, t);
+        }
 #pragma unroll
         for (int nt = 0; nt < 8; nt++)
 #pragma unroll
-            for (int e = 0; e < 4; e++) {
-                const int cq = nt * 8 + 2 * t + (e & 1);             // query inside the tile
-                const int qi = i * BT + cq, ki = row0 + g + (e >> 1) * 8;
-                const float p = (i == kt && ki > qi) ? 0.0f : __expf(s[nt][e] * scale - sL[cq]);
-                s[nt][e] = p;                                         // P^T
-                dp[nt][e] = p * (dp[nt][e] - sD[cq]) * scale;         // dS^T
-            }
-        stage(myP, s, g, t);
+            for (int e = 0; e < 4; e++) s[nt][e] = ex2(__fmaf_rn(s[nt][e], sl2, -sL[nt * 8 + 2 * t + (e & 1)]));  // P^T
+        if (i == kt) {  // the diagonal tile: keys after the query have probability 0
+#pragma unroll
+            for (int nt = 0; nt < 8; nt++)
+#pragma unroll
+                for (int e = 0; e < 4; e++)
+                    if (warp * 16 + g + (e >> 1) * 8 > nt * 8 + 2 * t + (e & 1)) s[nt][e] = 0.0f;
+        }
+#pragma unroll
+        for (int nt = 0; nt < 8; nt++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) dp[nt][e] = s[nt][e] * (dp[nt][e] - sD[nt * 8 + 2 * t + (e & 1)]) * scale;  // dS^T
+        stage<X3>(myP, s, g, t);
         __syncwarp();
-        mma_p_tile(dv, myP, sO, S_NK, g, t);
+        gemm_sa<X3, false>(dv, myP, S_P, sO2, S_2, g, t);
         __syncwarp();
-        stage(myP, dp, g, t);
+        stage<X3>(myP, dp, g, t);
         __syncwarp();
-        mma_p_tile(dk, myP, sQ, S_NK, g, t);
+        gemm_sa<X3, false>(dk, myP, S_P, sQ2, S_2, g, t);
         __syncwarp();
     }
     float* k0 = dqkv + (int64_t)(b * T + row0 + g) * ld + (H + h) * HS;
@@ -335,9 +475,10 @@ __global__ void __launch_bounds__(kThreads) k_attn_bwd_dkv(const float* __restri
     }
 }
 
-constexpr size_t kFwdSmem = (size_t)(BT * S_NK + BT * S_KN + 4 * 16 * S_P) * sizeof(float);
-constexpr size_t kDqSmem = (size_t)(2 * BT * S_NK + 4 * 16 * S_P) * sizeof(float);
-constexpr size_t kDkvSmem = (size_t)(2 * BT * S_NK + 4 * 16 * S_P + 2 * BT) * sizeof(float);
+// Shared memory per block; the split-product kernels also keep their own side's tile(s) there.
+constexpr size_t fwd_smem(bool x3) { return (size_t)(BT * S_NK + BT * S_KN + 4 * 16 * S_P + (x3 ? BT * S_NK : 0)) * sizeof(float); }
+constexpr size_t dq_smem(bool x3) { return (size_t)(2 * BT * S_NK + 4 * 16 * S_P + (x3 ? 2 * BT * S_NK : BT * S_KN)) * sizeof(float); }
+constexpr size_t dkv_smem(bool x3) { return (size_t)(2 * BT * S_NK + 4 * 16 * S_P + 2 * BT + (x3 ? 2 * BT * S_NK : 2 * BT * S_KN)) * sizeof(float); }
 
 static bool allow(const void* kernel, size_t smem) {
     return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
@@ -346,6 +487,25 @@ static void report(cudaError_t e) {
     if (e != cudaSuccess) slb::Engine::get().set_error(slb::ERR_LAUNCH);
 }
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+static bool g_tf32 = false;  // sl_cuda_attention_set_tf32
+
+template <bool X3>
+static void forward(const float* qkv, float* out, float* L, int64_t B, int64_t T, int64_t H, float scale) {
+    static const bool ok = allow((const void*)k_attn_fwd<X3>, fwd_smem(X3));
+    if (!ok) return report(cudaErrorInvalidValue);
+    k_attn_fwd<X3><<<dim3((unsigned)(T / BT), (unsigned)(B * H)), kThreads, fwd_smem(X3)>>>(qkv, out, L, (int)T, (int)H, scale);
+    report(cudaPeekAtLastError());
+}
+template <bool X3>
+static void backward(const float* qkv, const float* L, const float* dout, const float* rowdot, float* dqkv, int64_t B, int64_t T,
+                     int64_t H, float scale) {
+    static const bool ok = allow((const void*)k_attn_bwd_dq<X3>, dq_smem(X3)) && allow((const void*)k_attn_bwd_dkv<X3>, dkv_smem(X3));
+    if (!ok) return report(cudaErrorInvalidValue);
+    const dim3 grid((unsigned)(T / BT), (unsigned)(B * H));
+    k_attn_bwd_dq<X3><<<grid, kThreads, dq_smem(X3)>>>(qkv, dout, L, rowdot, dqkv, (int)T, (int)H, scale);
+    k_attn_bwd_dkv<X3><<<grid, kThreads, dkv_smem(X3)>>>(qkv, dout, L, rowdot, dqkv, (int)T, (int)H, scale);
+    report(cudaPeekAtLastError());
+}
 
 }  // namespace slb_attn
 
@@ -353,16 +513,16 @@ using namespace slb_attn;
 
 extern "C" int sl_cuda_attention_supported(int64_t T, int64_t hs) { return hs == HS && T >= BT && T % BT == 0 ? 1 : 0; }
 
+extern "C" void sl_cuda_attention_set_tf32(int on) { g_tf32 = on != 0; }
+
 extern "C" void sl_cuda_attention(const float* qkv, float* out, float* L, int64_t B, int64_t T, int64_t H, int64_t hs,
                                   float scale, int64_t tile, float* s, float* acc, float* m, float* l, float* c,
                                   float* rowbuf, float* ones, void* ptrs) {
     (void)tile, (void)s, (void)acc, (void)m, (void)l, (void)c, (void)rowbuf, (void)ones, (void)ptrs;  // the reference's scratch: unused
     if (B <= 0 || H <= 0) return;
     if (!sl_cuda_attention_supported(T, hs) || !aligned16(qkv) || !aligned16(out)) return report(cudaErrorInvalidValue);
-    static const bool ok = allow((const void*)k_attn_fwd, kFwdSmem);
-    if (!ok) return report(cudaErrorInvalidValue);
-    k_attn_fwd<<<dim3((unsigned)(T / BT), (unsigned)(B * H)), kThreads, kFwdSmem>>>(qkv, out, L, (int)T, (int)H, scale);
-    report(cudaPeekAtLastError());
+    if (g_tf32) forward<false>(qkv, out, L, B, T, H, scale);
+    else forward<true>(qkv, out, L, B, T, H, scale);
 }
 
 extern "C" void sl_cuda_attention_bwd(const float* qkv, const float* out, const float* L, const float* dout, float* dqkv,
@@ -373,14 +533,11 @@ extern "C" void sl_cuda_attention_bwd(const float* qkv, const float* out, const 
     if (B <= 0 || H <= 0) return;
     if (!sl_cuda_attention_supported(T, hs) || !aligned16(qkv) || !aligned16(dout) || !aligned16(dqkv) || !oc)
         return report(cudaErrorInvalidValue);
-    static const bool ok = allow((const void*)k_attn_bwd_dq, kDqSmem) && allow((const void*)k_attn_bwd_dkv, kDkvSmem);
-    if (!ok) return report(cudaErrorInvalidValue);
     // `oc` (B * H * tile * 64 floats of the reference's scratch, tile >= 64) holds the B * H * T row dots
     float* rowdot = oc;
     const int64_t rows = B * T * H;
     k_attn_rowdot<<<(unsigned)((rows + kThreads / 32 - 1) / (kThreads / 32)), kThreads>>>(out, dout, rowdot, (int)B, (int)T, (int)H);
-    const dim3 grid((unsigned)(T / BT), (unsigned)(B * H));
-    k_attn_bwd_dq<<<grid, kThreads, kDqSmem>>>(qkv, dout, L, rowdot, dqkv, (int)T, (int)H, scale);
-    k_attn_bwd_dkv<<<grid, kThreads, kDkvSmem>>>(qkv, dout, L, rowdot, dqkv, (int)T, (int)H, scale);
     report(cudaPeekAtLastError());
+    if (g_tf32) backward<false>(qkv, L, dout, rowdot, dqkv, B, T, H, scale);
+    else backward<true>(qkv, L, dout, rowdot, dqkv, B, T, H, scale);
 }
