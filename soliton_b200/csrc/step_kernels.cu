@@ -9,7 +9,7 @@
 // so here each is ONE pass: a warp owns a row, holds it in registers (256-bit loads, c / 256 of them per lane and
 // tensor), reduces with shuffles, and writes the result once. The column sums of the backward pass (dw, db) are
 // accumulated per lane over the rows a warp walks, combined per block in shared memory in warp order, written as one
-// partial per block into the caller's scratch matrix, and added up over the blocks in block order by a second, tiny
+// partial per block into the caller's scratch matrix, and added up over the blocks in a fixed order by a second, tiny
 // launch: no atomics, the same bits on every run.
 //
 // Algorithmic traffic: forward 8 B per element (read x, write y), backward 12 B per element (read dy and x, write dx).
@@ -184,16 +184,27 @@ __global__ void __launch_bounds__(kThreads, K <= 3 ? 2 : 1) k_ln_bwd_vec(const f
     }
 }
 
-// dw[j], db[j] = partials of the blocks added in block order. One thread per column of dw and of db.
+// dw[j], db[j] = the partials of the blocks. A block owns 32 columns (of dw and db laid side by side); each of its
+// eight warps adds up every eighth block's partial, and the eight sums meet in shared memory in warp order: a fixed
+// order, so the same bits every run, with eight times the loads in flight of one thread per column.
 __global__ void __launch_bounds__(kThreads) k_ln_bwd_finish(const float* __restrict__ partial, int blocks, int64_t c,
                                                             float* __restrict__ dw, float* __restrict__ db) {
-    const int64_t j = (int64_t)blockIdx.x * kThreads + threadIdx.x;
-    if (j >= 2 * c) return;
+    __shared__ float part[kWarps][32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t j = (int64_t)blockIdx.x * 32 + lane;  // c is a multiple of 256 here: a block never straddles dw and db
     const int pass = j >= c;
     const int64_t col = j - pass * c;
     float t = 0;
-    for (int b = 0; b < blocks; b++) t += partial[((int64_t)b * 2 + pass) * c + col];
-    (pass ? db : dw)[col] = t;
+    if (j < 2 * c)
+        for (int b = warp; b < blocks; b += kWarps) t += partial[((int64_t)b * 2 + pass) * c + col];
+    part[warp][lane] = t;
+    __syncthreads();
+    if (warp == 0 && j < 2 * c) {
+        float sum = part[0][lane];
+#pragma unroll
+        for (int k = 1; k < kWarps; k++) sum += part[k][lane];
+        (pass ? db : dw)[col] = sum;
+    }
 }
 
 // Any c: a warp per row for dx, then a thread per column for dw and db, rows in order.
@@ -293,7 +304,7 @@ extern "C" void sl_cuda_layernorm_bwd(const float* dy, const float* x, const flo
             case 3: k_ln_bwd_vec<3><<<grid, kThreads>>>(dy, x, w, mean, invstd, dx, tmp, outer); break;
             default: k_ln_bwd_vec<4><<<grid, kThreads>>>(dy, x, w, mean, invstd, dx, tmp, outer); break;
         }
-        k_ln_bwd_finish<<<(unsigned)((2 * c + kThreads - 1) / kThreads), kThreads>>>(tmp, grid, c, dw, db);
+        k_ln_bwd_finish<<<(unsigned)((2 * c + 31) / 32), kThreads>>>(tmp, grid, c, dw, db);
     } else {
         k_ln_dx_any<<<row_grid(outer), kThreads>>>(dy, x, w, mean, invstd, dx, outer, c);
         k_ln_cols_any<<<(unsigned)((c + kThreads - 1) / kThreads), kThreads>>>(dy, x, mean, invstd, dw, db, outer, c);

@@ -2,7 +2,7 @@
 reference's own kernels (core/cuda/kernels.cu:385-449, built unmodified into oracle/_ref/) and against float64.
 
 Floating point: the reduction order differs from the reference's (a warp per row and a butterfly, where the reference
-reduces a block in two stages; column sums in fixed block order, where the reference calls cuBLAS), so results agree
+reduces a block in two stages; column sums in a fixed order over the blocks, where the reference calls cuBLAS), so results agree
 to rounding, not to the bit. The bars are the reference's own test bars (tests/test_ops.py:17-26): outputs
 rtol 1e-4 / atol 1e-4, gradients rtol 1e-3 / atol 1e-4 -- and, against the reference kernels on the same inputs, ten
 times tighter than that."""
