@@ -78,6 +78,7 @@ def parse():
     ap.add_argument("--bare", action="store_true", help="gradient mean only, no optimizer update (link-bound floor)")
     ap.add_argument("--attention", action="store_true", help="fused causal attention against the reference's TF32 path")
     ap.add_argument("--xent", action="store_true", help="cross entropy forward and backward against the reference's kernels")
+    ap.add_argument("--elementwise", action="store_true", help="binary ops and embedding backward against the reference's kernels")
     ap.add_argument("--layernorm", action="store_true", help="layer normalisation forward and backward against the reference's kernels")
     return ap.parse_args()
 
@@ -876,6 +877,74 @@ def run_xent(args):
     print(json.dumps({"metric": "cross_entropy_algorithmic_GBps", "hbm_peak": hbm, "hbm_peak_kind": hbm_kind, "rows": rows_out}), flush=True)
 
 
+def run_elementwise(args):
+    """Binary ops in the two shapes a GPT-2 step uses (residual add, bias add, 8,192 x 3,072 floats) and the
+    embedding's backward at GPT-2's sizes (8,192 tokens, 50,257 x 768 table), this library's kernels and the
+    reference's (core/cuda/kernels.cu:139-181, 459-487 from oracle/_ref/) on the same buffers, CUDA events, median of
+    20. GB/s are algorithmic: 12 bytes per element for the residual add, 8 for the bias add; for the embedding the
+    table written once plus the rows of dy read once."""
+    import numpy as np
+    import torch
+    from soliton_b200 import tensor as T
+    from soliton_b200._C import lib
+    T._dev(T.CUDA)
+    R = reference_gpu_lib()
+    C = ctypes
+    if R is not None:
+        assert R.sl_cuda_set_device(0) == 0
+        R.sl_cuda_binary.argtypes = [C.c_int] + [C.c_void_p] * 3 + [C.c_int] + [C.c_void_p] * 3
+        R.sl_cuda_embedding_bwd.argtypes = [C.c_void_p] * 3 + [C.c_int64] * 3 + [C.c_void_p] * 4 + [C.c_size_t]
+    hbm, hbm_kind = hbm_peak()
+
+    def timed(fn, reps=20):
+        out = []
+        for i in range(reps + 3):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            if i >= 3:
+                out.append(e0.elapsed_time(e1))
+        return statistics.median(out)
+
+    longs = lambda v: (C.c_int64 * len(v))(*v)  # noqa: E731
+    rows_out = []
+    rows, c = 8192, 3072
+    rng = np.random.default_rng(0)
+    a = T.tensor(rng.standard_normal((rows, c), dtype=np.float32), "cuda")
+    b = T.tensor(rng.standard_normal((rows, c), dtype=np.float32), "cuda")
+    bias = T.tensor(rng.standard_normal((c,), dtype=np.float32), "cuda")
+    o = T.empty((rows, c), "cuda")
+    n, vocab, width = 8192, 50257, 768
+    dy = T.tensor(rng.standard_normal((n, width), dtype=np.float32), "cuda")
+    idx = T.tensor(rng.integers(0, vocab, n).astype(np.int32).view(np.float32), "cuda")
+    dw = T.empty((vocab, width), "cuda")
+    keys, perm, perm_out = (T.empty((n,), "cuda") for _ in range(3))
+    temp_bytes = n * 16 + (1 << 20)
+    temp = T.empty((temp_bytes // 4,), "cuda")
+    T.synchronize()
+    shape, dense, suffix = longs((rows, c)), longs((c, 1)), longs((0, 1))
+    for name, Lib in (("this library", lib), ("reference", R)):
+        if Lib is None:
+            continue
+        t_res = timed(lambda: Lib.sl_cuda_binary(0, a.ptr, b.ptr, o.ptr, 2, shape, dense, dense))
+        t_bias = timed(lambda: Lib.sl_cuda_binary(0, a.ptr, bias.ptr, o.ptr, 2, shape, dense, suffix))
+        t_emb = timed(lambda: Lib.sl_cuda_embedding_bwd(dy.ptr, idx.ptr, dw.ptr, vocab, n, width, keys.ptr, perm.ptr, perm_out.ptr,
+                                                        temp.ptr, temp_bytes))
+        e = rows * c
+        emb_bytes = 4 * (vocab * width + n * width)
+        rows_out.append({"by": name, "residual_add_ms": round(t_res, 4), "residual_add_GBps": round(12 * e / t_res / 1e6, 1),
+                         "residual_add_frac_of_hbm": round(12 * e / t_res / 1e6 / hbm, 3),
+                         "bias_add_ms": round(t_bias, 4), "bias_add_GBps": round(8 * e / t_bias / 1e6, 1),
+                         "bias_add_frac_of_hbm": round(8 * e / t_bias / 1e6 / hbm, 3),
+                         "embedding_bwd_ms": round(t_emb, 4), "embedding_bwd_GBps": round(emb_bytes / t_emb / 1e6, 1),
+                         "embedding_bwd_frac_of_hbm": round(emb_bytes / t_emb / 1e6 / hbm, 3)})
+    assert lib.sl_check(T.CUDA) == 0
+    print(json.dumps({"metric": "elementwise_algorithmic_GBps", "hbm_peak": hbm, "hbm_peak_kind": hbm_kind, "rows": rows_out}), flush=True)
+
+
 def run_reference_gpu(args, rank, local_rank, world):
     """The reference's own GPU path as an arm of its own (the product arm also carries it as `gpu_baseline`)."""
     import torch
@@ -914,6 +983,8 @@ def main():
         return run_attention(args)
     if args.xent:
         return run_xent(args)
+    if args.elementwise:
+        return run_elementwise(args)
     if world == 1 and args.gpus > 1:
         # launched without torchrun: start one process per GPU ourselves
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",

@@ -201,6 +201,15 @@ bool fused_attention(int64_t B, int64_t T, int64_t H, int64_t hs, int64_t tile) 
     }();
     return !refused && sl_cuda_attention_supported(T, hs) && B * H * T <= B * H * tile * hs;
 }
+// SOLITON_FULLSTEP_ELT=reference: binary ops and the embedding's backward from the reference backend instead of this
+// library's kernels.
+bool reference_elementwise() {
+    static const bool wanted = [] {
+        const char* v = getenv("SOLITON_FULLSTEP_ELT");
+        return v && strcmp(v, "reference") == 0;
+    }();
+    return wanted;
+}
 // SOLITON_FULLSTEP_XENT=reference: cross entropy from the reference backend instead of this library's kernels.
 bool reference_xent() {
     static const bool wanted = [] {
@@ -224,7 +233,7 @@ void sl_set_tf32(int dev, int on) {
 // api.d:335-346
 void sl_binary(int dev, int op, const float* a, const float* b, float* o, int nd, const int64_t* shape, const int64_t* sa,
                const int64_t* sb) {
-    if (route(dev) == RUN) backend().binary(op, a, b, o, nd, shape, sa, sb);
+    if (route(dev) == RUN) (reference_elementwise() ? backend().binary : sl_cuda_binary)(op, a, b, o, nd, shape, sa, sb);
 }
 void sl_strided_copy(int dev, const float* src, int64_t base, float* o, int nd, const int64_t* shape, const int64_t* ss) {
     if (route(dev) == RUN) backend().strided_copy(src, base, o, nd, shape, ss);
@@ -345,7 +354,8 @@ int sl_embedding_bwd(int dev, const float* dy, const int* idx, float* dw, int64_
     int* perm_out = static_cast<int*>(s.bytes((size_t)n * sizeof(int)));
     void* temp = s.bytes(temp_bytes);
     if (!s.ok) return kOutOfMemory;
-    if (route(dev) == RUN) backend().embedding_bwd(dy, idx, dw, vocab, n, c, keys, perm, perm_out, temp, temp_bytes);
+    if (route(dev) == RUN)
+        (reference_elementwise() ? backend().embedding_bwd : sl_cuda_embedding_bwd)(dy, idx, dw, vocab, n, c, keys, perm, perm_out, temp, temp_bytes);
     return 0;
 }
 

@@ -162,6 +162,17 @@ void sl_cuda_attention_bwd(const float* qkv, const float* out, const float* L, c
  * overwrites its first 8 bytes. */
 double sl_cuda_cross_entropy(const float* logits, const int* t, int64_t n, int64_t v, float* rowloss);
 void sl_cuda_cross_entropy_bwd(const float* logits, const int* t, float* dl, int64_t n, int64_t v, float dloss);
+/* core/soliton/api.d:23-24,44-45 -> core/cuda/kernels.cu:139-181,459-487: out = a op b (op 0 add, 1 subtract,
+ * 2 multiply, 3 divide) over an output of up to 8 dimensions, the inputs given by their strides in elements (0 where
+ * they broadcast); and the embedding's backward: dw (vocab x c) = for every id the sum of the rows of dy (n x c)
+ * whose token has that id, rows added in token order. `keys`, `perm`, `perm_out` (n ints each) and `temp`
+ * (sl_cuda_sort_temp_bytes(n) bytes at the least, else sticky error 8) are the caller's scratch. Both give the
+ * reference's bits. */
+void sl_cuda_binary(int op, const float* a, const float* b, float* o, int nd, const int64_t* shape, const int64_t* sa,
+                    const int64_t* sb);
+size_t sl_cuda_sort_temp_bytes(int64_t n);
+void sl_cuda_embedding_bwd(const float* dy, const int* idx, float* dw, int64_t vocab, int64_t n, int64_t c, int* keys, int* perm,
+                           int* perm_out, void* temp, size_t temp_bytes);
 /* No counterpart in the reference; modelled on sl_cuda_set_workspace (core/cuda/kernels.cu:115). A host core that
  * owns the allocator hands the path its workspace (slb_workspace_bytes() bytes from its pool) once per device. */
 int sl_cuda_dp_set_workspace(void* p, size_t n);

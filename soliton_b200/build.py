@@ -10,7 +10,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libsoliton_b200.so")
-SOURCES = ["pool.cpp", "rendezvous.cpp", "dp_kernels.cu", "dp_engine.cu", "api.cu", "fabric_probe.cu", "step_kernels.cu", "attention_kernels.cu", "xent_kernels.cu"]
+SOURCES = ["pool.cpp", "rendezvous.cpp", "dp_kernels.cu", "dp_engine.cu", "api.cu", "fabric_probe.cu", "step_kernels.cu", "attention_kernels.cu", "xent_kernels.cu", "elementwise_kernels.cu"]
 HEADERS = ["pool.hpp", "rendezvous.hpp", "dp_types.h", "dp_launch.h", "dp_engine.hpp", "foreign_path.h",
            os.path.join("..", "..", "include", "soliton_b200.h")]
 NVCC_FLAGS = ["-std=c++17", "-O3", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",

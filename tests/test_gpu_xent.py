@@ -18,9 +18,11 @@ from tests.gpu_util import DevBuf, check_ok
 
 pytestmark = pytest.mark.gpu
 # (rows, v, skew of the logits, skew of the gradient): 50,257 is GPT-2's vocabulary -- an odd row length, so rows start
-# at all four alignments; n = 1 takes the host sum; unequal skews the scalar-store path
+# at all four alignments; n = 1 takes the host sum; unequal skews the scalar-store path. Backward: rows from 4,096
+# logits on are split over a cluster of 4 blocks (8 when a quarter exceeds 100 KB: 120,001), longer ones (250,007) and
+# shorter ones are read twice by one block
 SHAPES = [(64, 50257, 0, 0), (7, 1000, 0, 0), (3, 5, 0, 0), (1, 17, 0, 0), (128, 50304, 0, 0), (33, 4097, 1, 1), (33, 4097, 0, 3),
-          (9, 2, 0, 0), (5, 1, 0, 0)]
+          (9, 2, 0, 0), (5, 1, 0, 0), (5, 120001, 0, 0), (3, 250007, 0, 0)]
 
 
 @pytest.fixture(scope="module")
