@@ -881,8 +881,9 @@ def run_elementwise(args):
     """Binary ops in the two shapes a GPT-2 step uses (residual add, bias add, 8,192 x 3,072 floats) and the
     embedding's backward at GPT-2's sizes (8,192 tokens, 50,257 x 768 table), this library's kernels and the
     reference's (core/cuda/kernels.cu:139-181, 459-487 from oracle/_ref/) on the same buffers, CUDA events, median of
-    20. GB/s are algorithmic: 12 bytes per element for the residual add, 8 for the bias add; for the embedding the
-    table written once plus the rows of dy read once."""
+    20; GELU forward and backward on the same 8,192 x 3,072 floats. GB/s are algorithmic: 12 bytes per element for
+    the residual add and GELU's backward, 8 for the bias add and GELU; for the embedding the table written once plus
+    the rows of dy read once."""
     import numpy as np
     import torch
     from soliton_b200 import tensor as T
@@ -894,6 +895,8 @@ def run_elementwise(args):
         assert R.sl_cuda_set_device(0) == 0
         R.sl_cuda_binary.argtypes = [C.c_int] + [C.c_void_p] * 3 + [C.c_int] + [C.c_void_p] * 3
         R.sl_cuda_embedding_bwd.argtypes = [C.c_void_p] * 3 + [C.c_int64] * 3 + [C.c_void_p] * 4 + [C.c_size_t]
+        R.sl_cuda_gelu.argtypes = [C.c_void_p, C.c_void_p, C.c_int64]
+        R.sl_cuda_gelu_bwd.argtypes = [C.c_void_p] * 3 + [C.c_int64]
     hbm, hbm_kind = hbm_peak()
 
     def timed(fn, reps=20):
@@ -933,12 +936,16 @@ def run_elementwise(args):
         t_bias = timed(lambda: Lib.sl_cuda_binary(0, a.ptr, bias.ptr, o.ptr, 2, shape, dense, suffix))
         t_emb = timed(lambda: Lib.sl_cuda_embedding_bwd(dy.ptr, idx.ptr, dw.ptr, vocab, n, width, keys.ptr, perm.ptr, perm_out.ptr,
                                                         temp.ptr, temp_bytes))
+        t_gelu = timed(lambda: Lib.sl_cuda_gelu(a.ptr, o.ptr, rows * c))
+        t_gelu_bwd = timed(lambda: Lib.sl_cuda_gelu_bwd(a.ptr, b.ptr, o.ptr, rows * c))
         e = rows * c
         emb_bytes = 4 * (vocab * width + n * width)
         rows_out.append({"by": name, "residual_add_ms": round(t_res, 4), "residual_add_GBps": round(12 * e / t_res / 1e6, 1),
                          "residual_add_frac_of_hbm": round(12 * e / t_res / 1e6 / hbm, 3),
                          "bias_add_ms": round(t_bias, 4), "bias_add_GBps": round(8 * e / t_bias / 1e6, 1),
                          "bias_add_frac_of_hbm": round(8 * e / t_bias / 1e6 / hbm, 3),
+                         "gelu_ms": round(t_gelu, 4), "gelu_frac_of_hbm": round(8 * e / t_gelu / 1e6 / hbm, 3),
+                         "gelu_bwd_ms": round(t_gelu_bwd, 4), "gelu_bwd_frac_of_hbm": round(12 * e / t_gelu_bwd / 1e6 / hbm, 3),
                          "embedding_bwd_ms": round(t_emb, 4), "embedding_bwd_GBps": round(emb_bytes / t_emb / 1e6, 1),
                          "embedding_bwd_frac_of_hbm": round(emb_bytes / t_emb / 1e6 / hbm, 3)})
     assert lib.sl_check(T.CUDA) == 0

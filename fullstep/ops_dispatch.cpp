@@ -201,8 +201,8 @@ bool fused_attention(int64_t B, int64_t T, int64_t H, int64_t hs, int64_t tile) 
     }();
     return !refused && sl_cuda_attention_supported(T, hs) && B * H * T <= B * H * tile * hs;
 }
-// SOLITON_FULLSTEP_ELT=reference: binary ops and the embedding's backward from the reference backend instead of this
-// library's kernels.
+// SOLITON_FULLSTEP_ELT=reference: binary ops, GELU and the embedding's backward from the reference backend instead of
+// this library's kernels.
 bool reference_elementwise() {
     static const bool wanted = [] {
         const char* v = getenv("SOLITON_FULLSTEP_ELT");
@@ -288,10 +288,10 @@ int sl_softmax_bwd(int dev, const float* y, const float* dy, float* dx, int64_t 
 
 // api.d:417-425
 void sl_gelu(int dev, const float* x, float* y, int64_t n) {
-    if (route(dev) == RUN) backend().gelu(x, y, n);
+    if (route(dev) == RUN) (reference_elementwise() ? backend().gelu : sl_cuda_gelu)(x, y, n);
 }
 void sl_gelu_bwd(int dev, const float* x, const float* dy, float* dx, int64_t n) {
-    if (route(dev) == RUN) backend().gelu_bwd(x, dy, dx, n);
+    if (route(dev) == RUN) (reference_elementwise() ? backend().gelu_bwd : sl_cuda_gelu_bwd)(x, dy, dx, n);
 }
 
 // SOLITON_FULLSTEP_LN=reference: layer normalisation from the reference backend instead of this library's kernels.

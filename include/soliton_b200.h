@@ -171,6 +171,10 @@ void sl_cuda_cross_entropy_bwd(const float* logits, const int* t, float* dl, int
 void sl_cuda_binary(int op, const float* a, const float* b, float* o, int nd, const int64_t* shape, const int64_t* sa,
                     const int64_t* sb);
 size_t sl_cuda_sort_temp_bytes(int64_t n);
+/* core/soliton/api.d:30-31 -> core/cuda/kernels.cu:226-240: y = x * Phi(x) (the exact GELU, through erf) and its
+ * backward dx = dy * (Phi(x) + x * phi(x)), four elements per thread; the reference's bits. */
+void sl_cuda_gelu(const float* x, float* y, int64_t n);
+void sl_cuda_gelu_bwd(const float* x, const float* dy, float* dx, int64_t n);
 void sl_cuda_embedding_bwd(const float* dy, const int* idx, float* dw, int64_t vocab, int64_t n, int64_t c, int* keys, int* perm,
                            int* perm_out, void* temp, size_t temp_bytes);
 /* No counterpart in the reference; modelled on sl_cuda_set_workspace (core/cuda/kernels.cu:115). A host core that

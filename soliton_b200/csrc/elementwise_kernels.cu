@@ -1,8 +1,8 @@
-// Two more bandwidth-bound pieces of a Soliton training step: broadcasting binary ops and the embedding's backward.
+// More bandwidth-bound pieces of a Soliton training step: broadcasting binary ops, GELU, the embedding's backward.
 //
-// Same backend-level names and signatures as the reference's CUDA file (core/cuda/kernels.cu:139-181, 459-487), and
-// the same bits: each output element is one fp32 operation on the same two inputs (binary), or the same rows added
-// in the same order (embedding).
+// Same backend-level names and signatures as the reference's CUDA file (core/cuda/kernels.cu:139-181, 226-240,
+// 459-487), and the same bits: each output element is the same fp32 expression of the same inputs (binary, GELU),
+// or the same rows added in the same order (embedding).
 //
 // Binary ops. A GPT-2 step runs 49 of them, nearly all "suffix" cases: residual adds (both inputs shaped like the
 // output) and bias adds (one input is the output's trailing dimension). The reference gives each element a thread
@@ -79,6 +79,39 @@ static int64_t repeating_suffix(int nd, const int64_t* shape, const int64_t* str
     return dense;
 }
 
+// ---------------------------------------------------------------- GELU
+
+// The exact GELU, x * Phi(x) with Phi through erf, and its derivative Phi(x) + x * phi(x)
+// (core/cuda/kernels.cu:226-240), four elements per thread.
+__device__ __forceinline__ float gelu(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678f)); }
+__device__ __forceinline__ float gelu_grad(float x, float dy) {
+    const float cdf = 0.5f * (1.0f + erff(x * 0.70710678f));
+    const float pdf = expf(-0.5f * x * x) * 0.39894228f;
+    return dy * (cdf + x * pdf);
+}
+__global__ void __launch_bounds__(kThreads) k_gelu4(int64_t n4, const float4* __restrict__ x, float4* __restrict__ y) {
+    const int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (i >= n4) return;
+    const float4 v = x[i];
+    y[i] = make_float4(gelu(v.x), gelu(v.y), gelu(v.z), gelu(v.w));
+}
+__global__ void __launch_bounds__(kThreads) k_gelu1(int64_t n, const float* __restrict__ x, float* __restrict__ y) {
+    const int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (i < n) y[i] = gelu(x[i]);
+}
+__global__ void __launch_bounds__(kThreads) k_gelu_bwd4(int64_t n4, const float4* __restrict__ x, const float4* __restrict__ dy,
+                                                        float4* __restrict__ dx) {
+    const int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (i >= n4) return;
+    const float4 v = x[i], g = dy[i];
+    dx[i] = make_float4(gelu_grad(v.x, g.x), gelu_grad(v.y, g.y), gelu_grad(v.z, g.z), gelu_grad(v.w, g.w));
+}
+__global__ void __launch_bounds__(kThreads) k_gelu_bwd1(int64_t n, const float* __restrict__ x, const float* __restrict__ dy,
+                                                        float* __restrict__ dx) {
+    const int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (i < n) dx[i] = gelu_grad(x[i], dy[i]);
+}
+
 // ---------------------------------------------------------------- embedding backward
 
 __global__ void __launch_bounds__(kThreads) k_fill4(float4* __restrict__ p, int64_t n4, float4 v) {
@@ -141,6 +174,25 @@ extern "C" void sl_cuda_binary(int op, const float* a, const float* b, float* o,
         for (int k = 0; k < nd; k++) d.shape[k] = shape[k], d.sa[k] = sa[k], d.sb[k] = sb[k];
         k_binary_strided<<<blocks_for(n), kThreads>>>(n, op, a, b, o, d);
     }
+    report(cudaPeekAtLastError(), slb::ERR_LAUNCH);
+}
+
+extern "C" void sl_cuda_gelu(const float* x, float* y, int64_t n) {
+    if (n <= 0) return;
+    if (n % 4 == 0 && aligned16(x) && aligned16(y))
+        k_gelu4<<<blocks_for(n / 4), kThreads>>>(n / 4, reinterpret_cast<const float4*>(x), reinterpret_cast<float4*>(y));
+    else
+        k_gelu1<<<blocks_for(n), kThreads>>>(n, x, y);
+    report(cudaPeekAtLastError(), slb::ERR_LAUNCH);
+}
+
+extern "C" void sl_cuda_gelu_bwd(const float* x, const float* dy, float* dx, int64_t n) {
+    if (n <= 0) return;
+    if (n % 4 == 0 && aligned16(x) && aligned16(dy) && aligned16(dx))
+        k_gelu_bwd4<<<blocks_for(n / 4), kThreads>>>(n / 4, reinterpret_cast<const float4*>(x), reinterpret_cast<const float4*>(dy),
+                                                    reinterpret_cast<float4*>(dx));
+    else
+        k_gelu_bwd1<<<blocks_for(n), kThreads>>>(n, x, dy, dx);
     report(cudaPeekAtLastError(), slb::ERR_LAUNCH);
 }
 

@@ -1,10 +1,13 @@
-"""Broadcasting binary ops and the embedding's backward (csrc/elementwise_kernels.cu), through the backend-level C ABI,
-against the reference's own kernels (core/cuda/kernels.cu:139-181, 459-487, built unmodified into oracle/_ref/) and
-against numpy.
+"""Broadcasting binary ops, GELU and the embedding's backward (csrc/elementwise_kernels.cu), through the backend-level
+C ABI, against the reference's own kernels (core/cuda/kernels.cu:139-181, 226-240, 459-487, built unmodified into
+oracle/_ref/) and against numpy.
 
 Bit-exact: a binary op is one IEEE fp32 operation per element on the same two inputs, so the reference, numpy's
 float32 arithmetic and these kernels must agree in every bit; the embedding's backward adds the same rows in the same
-(token) order as the reference, so its sums agree in every bit with the reference and to rounding with float64."""
+(token) order as the reference, so its sums agree in every bit with the reference and to rounding with float64. GELU
+is the same fp32 expression through the same erf and exp of the CUDA math library: the reference's bits, and float64's
+(math.erf) to 1e-6, the reference's own bar for unary ops being rtol 1e-4 (tests/test_ops.py)."""
+import math
 import ctypes as C
 import os
 
@@ -30,6 +33,10 @@ def ref(cuda):
     r.sl_cuda_binary.restype = None
     r.sl_cuda_embedding_bwd.argtypes = [P, P, P, L, L, L, P, P, P, P, C.c_size_t]
     r.sl_cuda_embedding_bwd.restype = None
+    r.sl_cuda_gelu.argtypes = [P, P, L]
+    r.sl_cuda_gelu.restype = None
+    r.sl_cuda_gelu_bwd.argtypes = [P, P, P, L]
+    r.sl_cuda_gelu_bwd.restype = None
     return r
 
 
@@ -101,6 +108,31 @@ def test_binary_refuses_what_it_cannot_index(cuda):
     lib.slb_clear_error()
     lib.sl_cuda_binary(0, buf.ptr, buf.ptr, buf.ptr, 2, longs((0, 4)), longs((4, 1)), longs((4, 1)))  # empty: nothing to do
     check_ok()
+
+
+@pytest.mark.parametrize("n,skew", [(8192 * 3072, 0), (1000, 0), (1001, 0), (4096, 1), (3, 0)])
+def test_gelu_gives_the_reference_bits(ref, n, skew):
+    rng = np.random.default_rng(n)
+    x = (rng.standard_normal(n) * 2.5).astype(np.float32)
+    x[:3] = [0.0, -12.0, 12.0][: min(3, n)]
+    dy = rng.standard_normal(n).astype(np.float32)
+    dx_, ddy = DevBuf(x, skew=skew), DevBuf(dy, skew=skew)
+    got = {}
+    for name, L_ in (("ours", lib), ("reference", ref)):
+        y, dx = DevBuf(n=n, skew=skew), DevBuf(n=n, skew=skew)
+        L_.sl_cuda_gelu(dx_.ptr, y.ptr, n)
+        L_.sl_cuda_gelu_bwd(dx_.ptr, ddy.ptr, dx.ptr, n)
+        check_ok()
+        got[name] = (y.get(), dx.get())
+    assert ref.sl_cuda_check() == 0
+    for mine, theirs in zip(got["ours"], got["reference"]):
+        np.testing.assert_array_equal(mine.view(np.uint32), theirs.view(np.uint32))
+    m = min(n, 20000)
+    x64 = x[:m].astype(np.float64)
+    cdf = 0.5 * (1.0 + np.array([math.erf(v / math.sqrt(2.0)) for v in x64]))
+    pdf = np.exp(-0.5 * x64 * x64) / math.sqrt(2.0 * math.pi)
+    np.testing.assert_allclose(got["ours"][0][:m], x64 * cdf, rtol=1e-6, atol=1e-6)
+    np.testing.assert_allclose(got["ours"][1][:m], dy[:m] * (cdf + x64 * pdf), rtol=1e-6, atol=1e-6)
 
 
 # (tokens, vocabulary, columns, how the ids are drawn)
