@@ -7,7 +7,7 @@ not part of the source tree (git-ignored):
     fullstep/_ref/gpt2.pyc                        the reference's example model and trainer, compiled, unmodified
     fullstep/_ref/reftests/*.pyc                  the reference's own tests, compiled, unmodified
 
-The Python parts need a reference checkout (SOLITON_REFERENCE, default /root/reference): nothing of it is copied as
+The Python parts need a reference checkout (environment variable SOLITON_REFERENCE): nothing of it is copied as
 source, only compiled. Where no checkout is present the existing outputs are used as they are.
 
     python fullstep/build.py
