@@ -58,7 +58,7 @@ PARITY_SHAPES = [(1000, 1200), (1200,), (300, 1000), (1000,), (3,), (2048 * 50,)
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-gpu"])
     ap.add_argument("--model", default="124M", choices=["124M", "medium", "tiny"])
