@@ -171,7 +171,11 @@ void sl_cuda_cross_entropy_bwd(const float* logits, const int* t, float* dl, int
 void sl_cuda_binary(int op, const float* a, const float* b, float* o, int nd, const int64_t* shape, const int64_t* sa,
                     const int64_t* sb);
 size_t sl_cuda_sort_temp_bytes(int64_t n);
-/* core/soliton/api.d:30-31 -> core/cuda/kernels.cu:226-240: y = x * Phi(x) (the exact GELU, through erf) and its
+/* Host only, for tests: which kernel sl_cuda_binary picks (2 = 128-bit suffix, 1 = element-wise suffix, 0 = general
+ * strides, -1 = refused) and, in out[0..1], how many elements of a and of b repeat (-1: not a repeating suffix). The
+ * classification is the reference's suffix_numel (core/cuda/kernels.cu:154-169). */
+int slb_binary_plan(int nd, const int64_t* shape, const int64_t* sa, const int64_t* sb, int64_t* out);
+/* core/soliton/api.d:36-37 -> core/cuda/kernels.cu:226-240: y = x * Phi(x) (the exact GELU, through erf) and its
  * backward dx = dy * (Phi(x) + x * phi(x)), four elements per thread; the reference's bits. */
 void sl_cuda_gelu(const float* x, float* y, int64_t n);
 void sl_cuda_gelu_bwd(const float* x, const float* dy, float* dx, int64_t n);

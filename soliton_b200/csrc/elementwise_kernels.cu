@@ -154,15 +154,30 @@ static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 using namespace slb_elt;
 
+// Which kernel sl_cuda_binary picks for these shapes and strides, without launching anything: 2 = 128-bit suffix
+// kernel, 1 = element-wise suffix kernel, 0 = general strides, -1 = refused; out[0], out[1] = the repeat lengths of a
+// and b (-1 where an input is no repeating suffix). Pointers are taken as 16-byte aligned.
+extern "C" int slb_binary_plan(int nd, const int64_t* shape, const int64_t* sa, const int64_t* sb, int64_t* out) {
+    if (nd < 0 || nd > kMaxDims) return -1;
+    int64_t n = 1;
+    for (int d = 0; d < nd; d++) n *= shape[d];
+    const int64_t na = repeating_suffix(nd, shape, sa), nb = repeating_suffix(nd, shape, sb);
+    if (out) out[0] = na, out[1] = nb;
+    if (!(na > 0 && nb > 0)) return 0;
+    return n % 4 == 0 && na % 4 == 0 && nb % 4 == 0 && n / 4 < ((int64_t)1 << 32) - kThreads ? 2 : 1;
+}
+
 extern "C" void sl_cuda_binary(int op, const float* a, const float* b, float* o, int nd, const int64_t* shape,
                                const int64_t* sa, const int64_t* sb) {
     if (nd < 0 || nd > kMaxDims || op < 0 || op > 3) return report(cudaErrorInvalidValue, slb::ERR_BAD_ARG);
     int64_t n = 1;
     for (int d = 0; d < nd; d++) n *= shape[d];
     if (n <= 0) return;
-    const int64_t na = repeating_suffix(nd, shape, sa), nb = repeating_suffix(nd, shape, sb);
-    if (na > 0 && nb > 0) {
-        if (n % 4 == 0 && na % 4 == 0 && nb % 4 == 0 && n / 4 < ((int64_t)1 << 32) - kThreads && aligned16(a) && aligned16(b) && aligned16(o))
+    int64_t rep[2];
+    const int plan = slb_binary_plan(nd, shape, sa, sb, rep);
+    const int64_t na = rep[0], nb = rep[1];
+    if (plan > 0) {
+        if (plan == 2 && aligned16(a) && aligned16(b) && aligned16(o))
             k_binary_suffix4<<<blocks_for(n / 4), kThreads>>>((unsigned)(n / 4), op, reinterpret_cast<const float4*>(a),
                                                              reinterpret_cast<const float4*>(b), reinterpret_cast<float4*>(o),
                                                              (unsigned)(na / 4), (unsigned)(nb / 4));
