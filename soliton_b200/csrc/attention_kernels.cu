@@ -1,14 +1,22 @@
-// Fused causal attention for the TF32 matmul regime, forward and backward, head size 64.
+// Fused causal attention, forward and backward, head size 64, in both precisions of the reference's matmuls.
 //
 // Same backend-level names and scratch arguments as the reference's CUDA file (core/cuda/kernels.cu:536-692). The
 // reference tiles at 256 and keeps every score tile in HBM between cuBLAS batched GEMMs and a dozen elementwise
 // launches per tile pair; with TF32 enabled that is about 37 % of a GPT-2 124M training step. Here a block owns 64
 // query rows (forward, dQ) or 64 key rows (dK, dV), walks the other side in tiles of 64, and keeps scores,
 // probabilities and accumulators in registers; only Q, K, V, dO come from memory, only O, L and the gradients go back.
-// Products run on the tensor cores with TF32 operands and fp32 accumulation (warp-level mma, m16n8k8), the same
-// arithmetic class as cuBLAS in the reference's TF32 mode (sl_set_tf32); without TF32 the caller keeps the
-// reference's path. Backward is two kernels -- one accumulates dQ over the key tiles, one dK and dV over the query
-// tiles -- so that no atomic is needed and every gradient has one fixed summation order: the same bits every run.
+// Products run on the tensor cores (warp-level mma, m16n8k8, TF32 operands, fp32 accumulation) in one of two ways,
+// chosen like the reference's matmul mode (sl_cuda_attention_set_tf32, next to sl_cuda_set_tf32):
+//   TF32 (template X3 = false): operands rounded to TF32 once, as cuBLAS does in the reference's TF32 mode;
+//   fp32 class (X3 = true, the default): operands stay fp32 in shared memory and are split as they are read into
+//     a TF32 head and a TF32 remainder, x = hi + lo to about 2^-22; a product is lo*hi + hi*lo + hi*hi, smallest
+//     terms first. Three tensor-core products instead of one, an error of about 2^-21 per operand pair.
+// Backward is two kernels -- one accumulates dQ over the key tiles, one dK and dV over the query tiles -- so that no
+// atomic is needed and every gradient has one fixed summation order: the same bits every run.
+//
+// What bounds the TF32 kernels is shared-memory bandwidth, not the tensor pipe (40-43 % busy): a warp-level product
+// takes two 32-bit shared loads per lane for its B operand. This is the legacy tensor path; tcgen05 with operands
+// delivered by TMA and accumulators in tensor memory is the way past that ceiling and is not what this file does.
 //
 // Layouts (core/cuda/kernels.cu:538-540, 614-692): qkv and dqkv packed (B, T, 3, H, 64); out and dout (B, T, H, 64);
 // L (B, H, T) = row maximum + log of the softmax denominator of the scaled, masked scores.
