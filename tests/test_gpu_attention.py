@@ -18,6 +18,7 @@ import numpy as np
 import pytest
 
 from oracle import build as obuild
+from oracle import step_ops
 from soliton_b200._C import lib
 from tests.gpu_util import DevBuf, check_ok
 
@@ -47,24 +48,9 @@ def ref(cuda):
 
 
 def truth(qkv, dout, scale):
-    """float64: out, L, dqkv for qkv (B, T, 3, H, hs), dout (B, T, H, hs)."""
-    qkv, dout = qkv.astype(np.float64), dout.astype(np.float64)
-    q, k, v = (qkv[:, :, i].transpose(0, 2, 1, 3) for i in range(3))  # (B, H, T, hs)
-    do = dout.transpose(0, 2, 1, 3)
-    T = q.shape[2]
-    s = scale * q @ k.transpose(0, 1, 3, 2)
-    s = np.where(np.tril(np.ones((T, T), bool)), s, -np.inf)
-    m = s.max(axis=-1, keepdims=True)
-    e = np.exp(s - m)
-    l = e.sum(axis=-1, keepdims=True)
-    p = e / l
-    o = p @ v
-    dv = p.transpose(0, 1, 3, 2) @ do
-    dp = do @ v.transpose(0, 1, 3, 2)
-    ds = p * (dp - (do * o).sum(axis=-1, keepdims=True)) * scale
-    dq, dk = ds @ k, ds.transpose(0, 1, 3, 2) @ q
-    dqkv = np.stack([g.transpose(0, 2, 1, 3) for g in (dq, dk, dv)], axis=2)
-    return o.transpose(0, 2, 1, 3), (m + np.log(l))[..., 0], dqkv
+    """float64: out, L, dqkv for qkv (B, T, 3, H, hs), dout (B, T, H, hs): the restatement of the reference's host
+    twin (pinned against PyTorch in tests/test_step_ops_oracle.py)."""
+    return step_ops.attention(qkv, dout, scale)
 
 
 def chunks_for(dim):

@@ -6,8 +6,7 @@ Bit-exact: a binary op is one IEEE fp32 operation per element on the same two in
 float32 arithmetic and these kernels must agree in every bit; the embedding's backward adds the same rows in the same
 (token) order as the reference, so its sums agree in every bit with the reference and to rounding with float64. GELU
 is the same fp32 expression through the same erf and exp of the CUDA math library: the reference's bits, and float64's
-(math.erf) to 1e-6, the reference's own bar for unary ops being rtol 1e-4 (tests/test_ops.py)."""
-import math
+(oracle/step_ops.py) to 1e-6, the reference's own bar for unary ops being rtol 1e-4 (tests/test_ops.py)."""
 import ctypes as C
 import os
 
@@ -15,6 +14,7 @@ import numpy as np
 import pytest
 
 from oracle import build as obuild
+from oracle import step_ops
 from soliton_b200._C import lib
 from tests.gpu_util import DevBuf, check_ok
 
@@ -85,9 +85,9 @@ def test_binary_gives_the_reference_bits(ref, op, out_shape, a_shape, b_shape, s
         check_ok()
         got[name] = out.get().reshape(out_shape)
     assert ref.sl_cuda_check() == 0
-    want = [np.add, np.subtract, np.multiply, np.divide][op](np.broadcast_to(a, out_shape), np.broadcast_to(b, out_shape))
+    want = np.broadcast_to(step_ops.binary(op, a, b), out_shape)
     np.testing.assert_array_equal(got["ours"].view(np.uint32), got["reference"].view(np.uint32))
-    np.testing.assert_array_equal(got["ours"].view(np.uint32), want.astype(np.float32).view(np.uint32))
+    np.testing.assert_array_equal(got["ours"].view(np.uint32), np.ascontiguousarray(want).view(np.uint32))
 
 
 def test_binary_with_a_transposed_input(ref):
@@ -128,11 +128,9 @@ def test_gelu_gives_the_reference_bits(ref, n, skew):
     for mine, theirs in zip(got["ours"], got["reference"]):
         np.testing.assert_array_equal(mine.view(np.uint32), theirs.view(np.uint32))
     m = min(n, 20000)
-    x64 = x[:m].astype(np.float64)
-    cdf = 0.5 * (1.0 + np.array([math.erf(v / math.sqrt(2.0)) for v in x64]))
-    pdf = np.exp(-0.5 * x64 * x64) / math.sqrt(2.0 * math.pi)
-    np.testing.assert_allclose(got["ours"][0][:m], x64 * cdf, rtol=1e-6, atol=1e-6)
-    np.testing.assert_allclose(got["ours"][1][:m], dy[:m] * (cdf + x64 * pdf), rtol=1e-6, atol=1e-6)
+    want_y, want_dx = step_ops.gelu(x[:m], dy[:m])
+    np.testing.assert_allclose(got["ours"][0][:m], want_y, rtol=1e-6, atol=1e-6)
+    np.testing.assert_allclose(got["ours"][1][:m], want_dx, rtol=1e-6, atol=1e-6)
 
 
 # (tokens, vocabulary, columns, how the ids are drawn)
@@ -162,9 +160,7 @@ def test_embedding_backward_gives_the_reference_bits(ref, n, vocab, c, draw):
         got[name] = dw.get().reshape(vocab, c)
     assert ref.sl_cuda_check() == 0
     np.testing.assert_array_equal(got["ours"].view(np.uint32), got["reference"].view(np.uint32))
-    want = np.zeros((vocab, c), np.float64)
-    np.add.at(want, idx, dy.astype(np.float64))
-    np.testing.assert_allclose(got["ours"], want, rtol=1e-5, atol=1e-5 * np.sqrt(n))
+    np.testing.assert_allclose(got["ours"], step_ops.embedding_bwd(idx, dy, vocab), rtol=1e-5, atol=1e-5 * np.sqrt(n))
 
 
 def test_embedding_backward_reports_too_little_sort_space(cuda):
